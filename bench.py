@@ -1,0 +1,372 @@
+#!/usr/bin/env python
+"""Benchmark of the SpMM / SDDMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (``config.workload``): benchmark configuration 2 of BASELINE.json — fp32 SDDMM
+over a 4096x4096 mask at 95 % sparsity (K = 64) followed by the SpMM of that CSR with V
+(4096x64).  One STEP is one pass of that chain over a batch of ``instances`` independent
+seeded instances whose combined inputs exceed the 126 MB L2, so every launch streams its
+operands from HBM (``config.l2_policy``).  Rows/instances are independent, so N GPUs each
+take their own batch of instances with no collective on the data path (weak scaling).
+
+Printed: ONE JSON line.  ``value`` is useful GFLOP/s (2*nnz*K per SDDMM + 2*nnz*N per SpMM)
+of the whole job with inputs resident in HBM; ``e2e`` is the same metric through the public
+torch operators with pinned HOST inputs copied to the device and the result copied back
+inside the timed region; ``roofline`` is for the kernel that takes most of the step;
+``cpu_baseline`` is the torch CPU path (torch.sparse.sampled_addmm + torch.sparse.mm) timed
+on this box's host cores on a bounded sample.  ``--impl reference`` times that CPU path as
+the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+if REPO not in sys.path:
+    sys.path.insert(0, REPO)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+M, N_COLS, K_DIM, DENSITY = 4096, 4096, 64, 0.05
+INSTANCES = 24  # per GPU; ~11 MB of operands each => ~270 MB per step, > L2 (126 MB)
+METRIC = "spmm_sddmm_gflops"
+UNIT = "GFLOP/s"
+
+
+def measured_peak_gbs():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def config_dict(n_gpus: int) -> dict:
+    return {
+        "workload": "cfg2: fp32 SDDMM 4096x4096 mask @95% sparsity, K=64, then SpMM x V 4096x64",
+        "instances_per_gpu": INSTANCES,
+        "l2_policy": "inputs larger than L2: each step streams %d independent instances (~270 MB)" % INSTANCES,
+        "index_dtype": "int32",
+        "parallelism": "independent instances per GPU, no collective" if n_gpus > 1 else "single GPU",
+    }
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        self.file.close()
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_instances(rank: int, count: int):
+    from intrasm_engine_b200 import synthetic as syn
+    return [syn.sddmm_chain_case(1000 * rank + i, M, N_COLS, K_DIM, DENSITY) for i in range(count)]
+
+
+def flops_of(inst) -> int:
+    from intrasm_engine_b200 import synthetic as syn
+    mask = inst[0]
+    return syn.sddmm_flops(mask.nnz, K_DIM) + syn.spmm_flops(mask.nnz, K_DIM)
+
+
+# ----------------------------------------------------------------------------------------
+# CPU path (reference arm and cpu_baseline)
+# ----------------------------------------------------------------------------------------
+
+def cpu_chain_seconds(inst, reps: int, warmup: int = 1):
+    """Median seconds of sampled_addmm + sparse.mm for one instance on all host threads."""
+    from oracle import oracle as orc
+    mask, q, k, v = inst
+    q_t, k_t, v_t = (torch.as_tensor(x) for x in (q, k, v))
+    zero = orc.torch_csr(mask.row_offsets, mask.column_indices,
+                         np.zeros(mask.nnz, np.float32), M, N_COLS)
+    kt = k_t.t().contiguous()
+    times = []
+    for it in range(warmup + reps):
+        t0 = time.perf_counter()
+        scores = torch.sparse.sampled_addmm(zero, q_t, kt, beta=0.0)
+        torch.sparse.mm(scores, v_t)
+        if it >= warmup:
+            times.append(time.perf_counter() - t0)
+    return statistics.median(times), times
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import warnings
+    warnings.filterwarnings("ignore")
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample = 2
+    insts = make_instances(0, sample)
+    fl = sum(flops_of(i) for i in insts)
+    for _ in range(max(args.warmup, 1)):
+        for inst in insts:
+            cpu_chain_seconds(inst, 1, 0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for inst in insts:
+            cpu_chain_seconds(inst, 1, 0)
+    dt = time.perf_counter() - t0
+    value = fl * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config_dict(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{sample} of {INSTANCES} instances per step; torch.sparse.sampled_addmm + torch.sparse.mm (CSR, int32 indices), fp32"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------
+# GPU path
+# ----------------------------------------------------------------------------------------
+
+def run_ours(args) -> None:
+    import intrasm_engine_b200  # noqa: F401  (raises if the CUDA library is missing)
+    from intrasm_engine_b200 import _lib, synthetic as syn
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    insts = make_instances(rank, INSTANCES)
+    total_flops = sum(flops_of(i) for i in insts)
+
+    def up(a):
+        return torch.as_tensor(np.ascontiguousarray(a)).to(dev)
+
+    class Dev:
+        pass
+
+    dinst = []
+    for mask, q, k, v in insts:
+        d = Dev()
+        d.nnz = mask.nnz
+        d.ri, d.ro, d.ci = up(mask.row_indices), up(mask.row_offsets), up(mask.column_indices)
+        d.q, d.k, d.v = up(q), up(k), up(v)
+        d.scores = torch.empty(mask.nnz, dtype=torch.float32, device=dev)
+        d.out = torch.empty((M, K_DIM), dtype=torch.float32, device=dev)
+        dinst.append(d)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def sddmm_all():
+        for d in dinst:
+            _lib.call("iex_sddmm_f32", M, K_DIM, N_COLS, d.nnz, d.ri.data_ptr(), d.ro.data_ptr(),
+                      d.ci.data_ptr(), d.q.data_ptr(), d.k.data_ptr(), d.scores.data_ptr(), 1, 0, stream)
+
+    def spmm_all():
+        for d in dinst:
+            _lib.call("iex_spmm_f32", M, N_COLS, K_DIM, d.nnz, d.ri.data_ptr(), d.scores.data_ptr(), 0,
+                      d.ro.data_ptr(), d.ci.data_ptr(), d.v.data_ptr(), None, d.out.data_ptr(), 1, 0, stream)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        sddmm_all()
+        spmm_all()
+    barrier()
+
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for s in range(args.steps):
+        ev[s][0].record()
+        sddmm_all()
+        ev[s][1].record()
+        spmm_all()
+        ev[s][2].record()
+    stop.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    elapsed_ms = start.elapsed_time(stop)
+    sddmm_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / (args.steps * INSTANCES)
+    spmm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / (args.steps * INSTANCES)
+
+    # ---- end to end through the public torch operators, host buffers in, host result out
+    ops = torch.ops.iex_ops
+    host = []
+    for mask, q, k, v in insts:
+        host.append([torch.as_tensor(np.ascontiguousarray(x)).pin_memory()
+                     for x in (q, k, v, mask.row_indices, mask.row_offsets, mask.column_indices)])
+    host_out = [torch.empty((M, K_DIM), dtype=torch.float32).pin_memory() for _ in insts]
+    h2d = sum(sum(t.numel() * t.element_size() for t in h) for h in host)
+    d2h = sum(t.numel() * t.element_size() for t in host_out)
+
+    def e2e_step():
+        for h, ho in zip(host, host_out):
+            q, k, v, ri, ro, ci = (t.to(dev, non_blocking=True) for t in h)
+            scores = ops.sddmm_sputnik_atomic_upd_weight(q[None], k[None], ri, ro, ci)
+            out = ops.spmm_sputnik_reuse_weight(v[None], ri, scores, ro, ci, M)
+            ho.copy_(out[0], non_blocking=True)
+
+    for _ in range(min(args.warmup, 3)):
+        e2e_step()
+    barrier()
+    e_start = torch.cuda.Event(enable_timing=True)
+    e_stop = torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(1, min(args.steps, 10))
+    e_start.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop)
+
+    if dist is not None:
+        tt = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = float(tt[0]), float(tt[1])
+        fl = torch.tensor([float(total_flops)], device=dev, dtype=torch.float64)
+        dist.all_reduce(fl, op=dist.ReduceOp.SUM)
+        job_flops = float(fl[0])
+    else:
+        job_flops = float(total_flops)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    value = job_flops * args.steps / (elapsed_ms * 1e-3) / 1e9
+    e2e_value = job_flops * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    mean_nnz = sum(d.nnz for d in dinst) / INSTANCES
+    sddmm_bytes = syn.sddmm_bytes(M, N_COLS, K_DIM, mean_nnz)
+    spmm_bytes = syn.spmm_bytes(M, N_COLS, K_DIM, mean_nnz, 4, 4)
+    kernels = {
+        "sddmm_rowtile_kernel": {"ms": sddmm_ms, "bytes": sddmm_bytes,
+                                 "gflops": syn.sddmm_flops(mean_nnz, K_DIM) / (sddmm_ms * 1e-3) / 1e9},
+        "spmm_rowgroup_kernel": {"ms": spmm_ms, "bytes": spmm_bytes,
+                                 "gflops": syn.spmm_flops(mean_nnz, K_DIM) / (spmm_ms * 1e-3) / 1e9},
+    }
+    for kv in kernels.values():
+        kv["achieved_gbs"] = kv["bytes"] / (kv["ms"] * 1e-3) / 1e9
+        kv["frac_of_%s_hbm" % peak_kind] = kv["achieved_gbs"] / peak
+    dom = max(kernels, key=lambda kname: kernels[kname]["ms"])
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[dom]["achieved_gbs"] / peak,
+                "traffic": None, "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
+                "us_per_launch": kernels[dom]["ms"] * 1e3}
+
+    cpu = None
+    if world == 1 or rank == 0:
+        import warnings
+        warnings.filterwarnings("ignore")
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        med, times = cpu_chain_seconds(insts[0], reps=8, warmup=2)
+        cpu = {"value": flops_of(insts[0]) / med / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": "1 of %d instances, median of 8 runs after 2 warm-ups; torch.sparse.sampled_addmm + torch.sparse.mm fp32, int32 CSR" % INSTANCES,
+               "ms_per_instance": med * 1e3}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(world), "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "steps": e2e_steps},
+        "gpu_launches": args.steps * INSTANCES * 2, "clocks": clocks, "kernels": kernels,
+    }
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,101 @@
+/*
+ * iex_b200 — C ABI of the B200 (sm_100a) implementation of intrasm_engine's hot path:
+ * CSR SpMM, SDDMM, the dense fp16 linear and the fused sparse||dense layer.
+ *
+ * Plain pointers and sizes only.  All pointers are device pointers unless a comment says
+ * "host".  `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ * No entry point synchronises, allocates or frees unless its comment says so, so all of
+ * them may be called while the stream is being captured into a CUDA graph — the
+ * reference wraps these calls in capture_library_call_begin/end
+ * (intrasm_engine/pytorch/cpp_extensions/layers_and_funcs/sputnik.py:59-66).
+ *
+ * Return value: 0 on success; a positive value is the cudaError_t of the launch (the
+ * reference's launchers return cudaGetLastError(),
+ * intrasm_engine/pytorch/csrc/extensions/sputnik_spmm.cu.inc:359); a negative value is
+ * one of IEX_ERR_* (argument rejected before any launch).
+ */
+#ifndef IEX_B200_H_
+#define IEX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define IEX_API __attribute__((visibility("default")))
+#else
+#define IEX_API
+#endif
+
+#define IEX_OK 0
+#define IEX_ERR_BAD_ARG (-1)      /* null pointer, negative size, batch out of range   */
+#define IEX_ERR_UNSUPPORTED (-2)  /* shape outside what the kernel family implements   */
+#define IEX_ERR_TOO_LARGE (-3)    /* exceeds a fixed-size resource named in the comment */
+#define IEX_ERR_DRIVER (-4)       /* a driver entry point (tensor-map encode) failed   */
+#define IEX_ERR_TIMEOUT (-5)      /* a bounded device-side wait gave up (status word)  */
+
+/* Human-readable text for any return value above (static storage, never NULL). */
+IEX_API const char* iex_error_string(int status);
+
+/* Library version, and the SM architecture the kernels were compiled for (100). */
+IEX_API int iex_version(void);
+IEX_API int iex_compiled_sm(void);
+
+/* ------------------------------------------------------------------------------------
+ * CSR SpMM      out[z, r, :] = sum_{p in row r} values[p] * dense[z, col[p], :]
+ *
+ * Replaces my_sputnik::CudaSpmm2 / CudaSpmm3 / CudaSpmmBiasRelu{2,3}
+ * (intrasm_engine/pytorch/csrc/extensions.h:10-17, :28-29;
+ *  sputnik_spmm_host_func.cu.inc:118-218).
+ *   row_indices  int32[m]    row visiting order (rows by decreasing nnz)
+ *   row_offsets  int32[m+1]  column_indices int32[nnz]
+ *   values       fp32, shared by the batch (values_batch_stride = 0, the "reuse_weight"
+ *                stamp) or one vector per batch item (stride = nnz, the "atomic" stamp)
+ *   dense [batch,k,n], out [batch,m,n], row-major contiguous
+ *   bias  fp32[m] or NULL; when given, out = relu(sum + bias[r])
+ *   accumulate != 0: the result is added onto `out` with atomic adds (the reference's
+ *                atomic store, sputnik_spmm.cu.inc:287-290); 0: plain store.
+ * Without `accumulate` every output element is summed by one thread in storage order
+ * with fused multiply-adds, so results are deterministic and reproducible bit for bit.
+ * ------------------------------------------------------------------------------------ */
+IEX_API int iex_spmm_f32(int m, int k, int n, int nnz, const int32_t* row_indices,
+                 const float* values, long long values_batch_stride,
+                 const int32_t* row_offsets, const int32_t* column_indices,
+                 const float* dense, const float* bias, float* out, int batch,
+                 int accumulate, void* stream);
+
+/* fp16 storage, fp32 accumulate.  Replaces my_sputnik::CudaSpmm5 / CudaSpmmBiasRelu5
+ * (extensions.h:30; sputnik_spmm_host_func_half.cu.inc:3-63), whose column indices are
+ * 16-bit (sputnik_kernels.cpp:179-181).  Unlike the reference kernel, odd n, odd row
+ * lengths and odd row offsets are accepted.  `_i32` is the same kernel with 32-bit
+ * column indices (k may exceed 65535). values/dense/out are IEEE binary16. */
+IEX_API int iex_spmm_f16_i16(int m, int k, int n, int nnz, const int32_t* row_indices,
+                     const void* values, const int32_t* row_offsets,
+                     const uint16_t* column_indices, const void* dense, const float* bias,
+                     void* out, int batch, void* stream);
+IEX_API int iex_spmm_f16_i32(int m, int k, int n, int nnz, const int32_t* row_indices,
+                     const void* values, const int32_t* row_offsets,
+                     const int32_t* column_indices, const void* dense, const float* bias,
+                     void* out, int batch, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * SDDMM     out[p] = sum_z dot(lhs[z, row(p), :], rhs[z, col[p], :])   for every stored p
+ *
+ * Replaces my_sputnik::CudaSddmm2 (extensions.h:19-26, :31;
+ * sputnik_sddmm.cu.inc:186-233).  lhs [batch,m,k], rhs [batch,n,k], out fp32[nnz] in the
+ * order of column_indices.  The batch items are summed inside the kernel (the reference
+ * adds them with atomics into one vector, sputnik_sddmm.cu.inc:177-178).
+ * accumulate != 0 adds onto `out` (atomic adds); 0 overwrites it.
+ * ------------------------------------------------------------------------------------ */
+IEX_API int iex_sddmm_f32(int m, int k, int n, int nnz, const int32_t* row_indices,
+                  const int32_t* row_offsets, const int32_t* column_indices,
+                  const float* lhs, const float* rhs, float* out, int batch,
+                  int accumulate, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IEX_B200_H_ */

@@ -1,0 +1,71 @@
+"""ctypes binding of ``libiex_b200.so`` (the C ABI declared in ``include/iex_b200.h``).
+
+There is no fallback: if the library has not been built, importing this module raises.
+Build it with ``python -m intrasm_engine_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, "libiex_b200.so")
+
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_ptr = ctypes.c_void_p
+c_size = ctypes.c_size_t
+
+# name -> (restype, argtypes); must list every symbol the header declares.
+SIGNATURES = {
+    "iex_error_string": (ctypes.c_char_p, [c_int]),
+    "iex_version": (c_int, []),
+    "iex_compiled_sm": (c_int, []),
+    # m k n nnz row_indices values vstride row_offsets cols dense bias out batch accumulate stream
+    "iex_spmm_f32": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ll, c_ptr, c_ptr,
+                             c_ptr, c_ptr, c_ptr, c_int, c_int, c_ptr]),
+    # m k n nnz row_indices values row_offsets cols dense bias out batch stream
+    "iex_spmm_f16_i16": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr,
+                                 c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    "iex_spmm_f16_i32": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr,
+                                 c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    # m k n nnz row_indices row_offsets cols lhs rhs out batch accumulate stream
+    "iex_sddmm_f32": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                              c_ptr, c_int, c_int, c_ptr]),
+}
+
+
+class IexError(RuntimeError):
+    """A C-ABI entry point returned a non-zero status."""
+
+    def __init__(self, name: str, status: int, text: str):
+        super().__init__(f"{name} failed with status {status}: {text}")
+        self.status = status
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library has not been built. "
+            "Run `python -m intrasm_engine_b200.build` (needs nvcc). "
+            "There is no CPU or PyTorch fallback for these operators.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+lib = _load()
+
+
+def error_string(status: int) -> str:
+    return lib.iex_error_string(int(status)).decode()
+
+
+def call(name: str, *args) -> None:
+    """Call a status-returning entry point and raise ``IexError`` on failure."""
+    status = getattr(lib, name)(*args)
+    if status != 0:
+        raise IexError(name, status, error_string(status))

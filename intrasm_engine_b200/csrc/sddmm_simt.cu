@@ -1,0 +1,142 @@
+// Sampled dense-dense matmul on CUDA cores (sm_100a):
+//   out[p] = sum_z dot(lhs[z, row(p), :], rhs[z, col[p], :])   for every stored position p.
+//
+// Work decomposition
+//   * A sub-warp of W lanes owns one row of the mask and walks its nonzeros in tiles of W.
+//     The grid's y dimension splits long rows: sub-warp y takes tiles y, y+gridDim.y, ...
+//     The grid is sized from nnz/m, not from the dense column count, so no CTA starts
+//     only to find it has nothing to do.
+//   * Lane i reads 4 consecutive k-values (one 128-bit load) of the lhs row and of each
+//     gathered rhs row, so a rhs row is read as one coalesced segment.  Each lane keeps W
+//     partial dot products (packed f32x2 FMAs), one per nonzero of the tile.
+//   * A butterfly exchange (W-1 shuffles instead of W*log2 W) leaves lane i with the full
+//     dot product of nonzero i, and the tile's W results are stored as one coalesced row.
+//   * Batch items are summed inside the kernel, in batch order: deterministic.
+#include "common.cuh"
+
+namespace iex {
+namespace {
+
+template <int W, bool VEC>
+__global__ void __launch_bounds__(128)
+sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
+                     const int* __restrict__ row_offsets, const int* __restrict__ cols,
+                     const float* __restrict__ lhs, const float* __restrict__ rhs,
+                     float* __restrict__ out, int batch, int accumulate) {
+  constexpr int KV = VEC ? 4 : 1;  // k-values per lane per pass
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / W;
+  const int sl = lane % W;
+  const unsigned submask = (W == 32) ? 0xffffffffu : (((1u << (W & 31)) - 1u) << (sub * W));
+  const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int slot = warp * (32 / W) + sub;
+  if (slot >= m) return;
+
+  const int r = __ldg(row_indices + slot);
+  const int beg = __ldg(row_offsets + r);
+  const int end = __ldg(row_offsets + r + 1);
+
+  for (int p0 = beg + blockIdx.y * W; p0 < end; p0 += gridDim.y * W) {
+    const int count = min(W, end - p0);
+    const int my_col = (sl < count) ? __ldg(cols + p0 + sl) : 0;
+
+    float2 acc[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) acc[j] = make_float2(0.f, 0.f);
+
+    for (int z = 0; z < batch; ++z) {
+      const float* a_row = lhs + (static_cast<size_t>(z) * m + r) * k;
+      const float* b_base = rhs + static_cast<size_t>(z) * n * k;
+      for (int kc = 0; kc < k; kc += W * KV) {
+        const int kk = kc + sl * KV;
+        const bool in_k = kk < k;
+        float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
+        if (in_k) {
+          if constexpr (VEC) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(a_row + kk));
+            a01 = make_float2(a.x, a.y);
+            a23 = make_float2(a.z, a.w);
+          } else {
+            a01.x = __ldg(a_row + kk);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+          const int cj = __shfl_sync(submask, my_col, j, W);
+          if (j < count && in_k) {
+            const float* b_row = b_base + static_cast<size_t>(cj) * k + kk;
+            if constexpr (VEC) {
+              const float4 b = __ldg(reinterpret_cast<const float4*>(b_row));
+              acc[j] = ffma2(a01, make_float2(b.x, b.y), acc[j]);
+              acc[j] = ffma2(a23, make_float2(b.z, b.w), acc[j]);
+            } else {
+              acc[j].x = fmaf(a01.x, __ldg(b_row), acc[j].x);
+            }
+          }
+        }
+      }
+    }
+
+    // Butterfly: after the step with stride s a lane keeps the s partial sums whose
+    // nonzero index agrees with its own lane index in bit s.
+    float red[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) red[j] = acc[j].x + acc[j].y;
+#pragma unroll
+    for (int s = W / 2; s >= 1; s >>= 1) {
+      const bool upper = (sl & s) != 0;
+#pragma unroll
+      for (int i = 0; i < s; ++i) {
+        const float keep = upper ? red[i + s] : red[i];
+        const float send = upper ? red[i] : red[i + s];
+        red[i] = keep + __shfl_xor_sync(submask, send, s, W);
+      }
+    }
+    if (sl < count) {
+      if (accumulate) atomicAdd(out + p0 + sl, red[0]);
+      else out[p0 + sl] = red[0];
+    }
+  }
+}
+
+template <int W, bool VEC>
+int launch(int m, int k, int n, int nnz, const int* ri, const int* ro, const int* cols,
+           const float* lhs, const float* rhs, float* out, int batch, int accumulate,
+           cudaStream_t stream) {
+  constexpr int kRowsPerBlock = 4 * (32 / W);
+  // Split rows so that each sub-warp gets about two tiles of W nonzeros on average.
+  const long long avg = m > 0 ? (static_cast<long long>(nnz) + m - 1) / m : 0;
+  int split = static_cast<int>((avg + 2 * W - 1) / (2 * W));
+  split = split < 1 ? 1 : (split > 64 ? 64 : split);
+  dim3 grid((m + kRowsPerBlock - 1) / kRowsPerBlock, split, 1);
+  sddmm_rowtile_kernel<W, VEC><<<grid, 128, 0, stream>>>(m, k, n, ri, ro, cols, lhs, rhs,
+                                                         out, batch, accumulate);
+  return launch_status();
+}
+
+}  // namespace
+}  // namespace iex
+
+extern "C" int iex_sddmm_f32(int m, int k, int n, int nnz, const int32_t* row_indices,
+                             const int32_t* row_offsets, const int32_t* column_indices,
+                             const float* lhs, const float* rhs, float* out, int batch,
+                             int accumulate, void* stream) {
+  using namespace iex;
+  if (m < 0 || k < 0 || n < 0 || nnz < 0 || batch < 0) return IEX_ERR_BAD_ARG;
+  if (m == 0 || nnz == 0) return IEX_OK;
+  if (!row_indices || !row_offsets || !column_indices || !out) return IEX_ERR_BAD_ARG;
+  if (batch > 0 && k > 0 && (!lhs || !rhs)) return IEX_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = (k % 4 == 0) && aligned16(lhs) && aligned16(rhs);
+#define IEX_GO(W, VEC) \
+  return launch<W, VEC>(m, k, n, nnz, row_indices, row_offsets, column_indices, lhs, rhs, out, batch, accumulate, s)
+  if (vec) {
+    if (k <= 32) { IEX_GO(8, true); }
+    if (k <= 64) { IEX_GO(16, true); }
+    IEX_GO(32, true);
+  }
+  if (k <= 8) { IEX_GO(8, false); }
+  if (k <= 16) { IEX_GO(16, false); }
+  IEX_GO(32, false);
+#undef IEX_GO
+}
