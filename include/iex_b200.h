@@ -95,6 +95,52 @@ IEX_API int iex_sddmm_f32(int m, int k, int n, int nnz, const int32_t* row_indic
                   const float* lhs, const float* rhs, float* out, int batch,
                   int accumulate, void* stream);
 
+/* ------------------------------------------------------------------------------------
+ * Tensor-core (tcgen05 / TMEM / TMA) entry points, fp16 storage, fp32 accumulate.
+ * Shared limits: n (tokens) a multiple of 16 (dense) / 64 (sparse, fused) and <= 256;
+ * k a multiple of 8; operand base pointers 16-byte aligned.  Shapes outside these limits
+ * return IEX_ERR_UNSUPPORTED (the CUDA-core entry points above take any shape).
+ * A device-side wait that gives up leaves IEX_ERR_TIMEOUT in a status word that
+ * iex_last_device_status() reads back (it synchronises the device; not capturable).
+ * ------------------------------------------------------------------------------------ */
+
+/* Dense branch: out[t, f] = sum_c input[t, c] * weight[f, c]  (input @ weight^T).
+ * Replaces the cuBLAS call behind MyLinear.forward
+ * (intrasm_engine/pytorch/cpp_extensions/layers_and_funcs/torch.py:17) and the
+ * CUTLASS-Python / Triton dense paths (intrasm_engine/common/cutlass_utils.py:106-204,
+ * triton_utils.py:14-137).  input [tokens, in_features], weight [out_features,
+ * in_features], out [tokens, out_features], all row-major fp16. */
+IEX_API int iex_linear_f16(int tokens, int in_features, int out_features, const void* input,
+                           const void* weight, void* out, void* stream);
+
+/* CSR SpMM on tensor cores: out[r, :] = sum_p values[p] * dense[col[p], :].
+ * Same contract as iex_spmm_f16_i16 / _i32 with batch = 1 and no bias (replaces
+ * my_sputnik::CudaSpmm5, extensions.h:30), plus one precondition: column indices ascend
+ * inside each row.  Rows are taken in natural order in tiles of 128, so no row_indices
+ * argument.  index_bits is 16 or 32.  Meant for moderate sparsity, where expanding a row
+ * tile into a dense shared-memory operand costs less than gathering dense rows. */
+IEX_API int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                            const void* column_indices, int index_bits, const void* values,
+                            const void* dense, void* out, void* stream);
+
+/* Fused sparse || dense layer: ONE launch computes
+ *     out_sparse[r, t] = sum_p values[p] * x[col[p], t]        (CSR W_sparse [m_sparse, k])
+ *     out_dense        = weight [m_dense, k] times x           (dense)
+ * with x [k, n] read by both branches.  This is the kernel behind the pair function of
+ * MySpMM + MyLinear (intrasm_engine/pytorch/horizontal_rewriter.py:76-311), replacing the
+ * two-stream graph interleaving of tests/test_interleaving.py:434-476.
+ * out_dense is [n, m_dense] (tokens major, the MyLinear convention) when
+ * dense_out_tokens_major != 0, else [m_dense, n]. */
+IEX_API int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, int nnz,
+                                      const int32_t* row_offsets, const void* column_indices,
+                                      int index_bits, const void* values, const void* weight,
+                                      const void* x, void* out_sparse, void* out_dense,
+                                      int dense_out_tokens_major, void* stream);
+
+/* Last device-side failure recorded by any kernel of this library (0 = none).
+ * Synchronises the device.  clear != 0 resets the word. */
+IEX_API int iex_last_device_status(int clear);
+
 #ifdef __cplusplus
 }
 #endif

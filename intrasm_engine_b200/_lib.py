@@ -1,7 +1,7 @@
 """ctypes binding of ``libiex_b200.so`` (the C ABI declared in ``include/iex_b200.h``).
 
 There is no fallback: if the library has not been built, importing this module raises.
-Build it with ``python -m intrasm_engine_b200.build``.
+Build it with ``python intrasm_engine_b200/build.py``.
 """
 from __future__ import annotations
 
@@ -32,6 +32,16 @@ SIGNATURES = {
     # m k n nnz row_indices row_offsets cols lhs rhs out batch accumulate stream
     "iex_sddmm_f32": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                               c_ptr, c_int, c_int, c_ptr]),
+    # tokens in_features out_features input weight out stream
+    "iex_linear_f16": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr]),
+    # m k n nnz row_offsets cols index_bits values dense out stream
+    "iex_spmm_f16_tc": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
+                                c_ptr, c_ptr]),
+    # m_sparse m_dense k n nnz row_offsets cols index_bits values weight x out_sparse out_dense
+    # dense_out_tokens_major stream
+    "iex_fused_spmm_linear_f16": (c_int, [c_int, c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int,
+                                          c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    "iex_last_device_status": (c_int, [c_int]),
 }
 
 
@@ -47,7 +57,7 @@ def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
             f"{LIB_PATH} is missing: the CUDA library has not been built. "
-            "Run `python -m intrasm_engine_b200.build` (needs nvcc). "
+            "Run `python intrasm_engine_b200/build.py` (needs nvcc). "
             "There is no CPU or PyTorch fallback for these operators.")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SIGNATURES.items():

@@ -1,6 +1,7 @@
 """In-tree build of ``libiex_b200.so`` (the C-ABI CUDA library) for sm_100a with nvcc.
 
-``python -m intrasm_engine_b200.build`` compiles every ``csrc/*.cu`` to an object file
+``python intrasm_engine_b200/build.py`` (run as a script, so that it works before the
+library exists) compiles every ``csrc/*.cu`` to an object file
 under ``build/`` (one nvcc process per file, in parallel) and links them into
 ``intrasm_engine_b200/libiex_b200.so``.  The CUDA runtime is linked statically, so the
 library has no load-time dependency besides libc/libstdc++ and the driver.

@@ -1,0 +1,690 @@
+// Tensor-core (tcgen05 / TMEM / TMA) kernel for the fp16 branches of the hot path on sm_100a:
+//   * dense linear          D[f, t] = sum_c W[f, c] * X[c, t]          (W streamed by TMA)
+//   * CSR SpMM              D[r, t] = sum_p val[p] * X[col[p], t]      (CSR decoded to smem)
+//   * fused sparse || dense both of the above in ONE launch, sharing X.
+//
+// One persistent, warp-specialised CTA design serves all three.  A CTA walks a list of
+// work units; a unit is one 128-row tile of either branch over the whole K range.  Per
+// unit the CTA runs a ring of shared-memory stages, each holding a 128x128 fp16 A tile
+// and a 128xN fp16 B tile in the 128-byte-swizzled layout tcgen05.mma reads:
+//
+//   warp 0      TMA producer: B tile (activations X) for every unit, A tile (W) for dense
+//               units, with cp.async.bulk.tensor + mbarrier complete_tx.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=tokens, K=16) into a
+//               TMEM accumulator and releases stages with tcgen05.commit.
+//   warps 2-5   epilogue: tcgen05.ld the accumulator (lane = output row), convert to
+//               fp16, store.
+//   warps 6..   CSR decoders (sparse units): stream the rows' values and column indices
+//               with 128-bit loads straight from the CSR arrays (no re-packed format, no
+//               per-tile metadata: a cursor per row advances through the ascending column
+//               indices), and scatter them into the zero-filled A stage in the swizzled
+//               operand layout, then fence.proxy.async + mbarrier arrive.
+//
+// Dense units cost almost no instructions (TMA + MMA), sparse units are instruction-bound
+// in the decoders, and both are fed from HBM, so co-resident CTAs working on units of
+// different kinds overlap well: that is the horizontal fusion.  Units of the two kinds
+// alternate in the work list so that neighbouring CTAs (two per SM) hold one of each.
+//
+// Every wait on an mbarrier is bounded; when a wait gives up the CTA raises a shared
+// abort flag, records IEX_ERR_TIMEOUT in the status word, drains the copies it armed,
+// frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace iex {
+namespace tc {
+
+constexpr int BM = 128;                   // rows of A per unit (UMMA M)
+constexpr int BK = 128;                   // K per stage: two 64-element swizzle atoms
+constexpr int UMMA_K = 16;                // K per tcgen05.mma.kind::f16
+constexpr int A_ATOM_BYTES = BM * 128;    // [128 rows x 64 fp16]
+constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
+constexpr int kFirstDecodeWarp = 6;
+constexpr uint32_t kSpinLimit = 1u << 24;  // mbarrier polls before a wait gives up
+
+struct Params {
+  // dense branch: out[f * d_stride_m + t * d_stride_n]
+  int d_tiles, d_m;
+  __half* d_out;
+  long long d_stride_m, d_stride_n;
+  int d_b_mn;  // B operand of the dense branch is MN-major ([K, N]) instead of K-major ([N, K])
+  // sparse branch: out[r * n + t]
+  int s_tiles, s_m, s_nnz;
+  __half* s_out;
+  const int* s_row_offsets;
+  const void* s_cols;
+  const __half* s_values;
+  // shared
+  int k, n;
+  int num_stages, tmem_cols;
+  int* status;
+};
+
+__device__ int g_status = 0;  // last device-side failure (IEX_ERR_TIMEOUT) of this library
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when the wait gave up or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      __nanosleep(32);
+    }
+  }
+  *abort_flag = 1;
+  atomicExch(status, IEX_ERR_TIMEOUT);
+  atomicExch(&g_status, IEX_ERR_TIMEOUT);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// lbo/sbo in bytes.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) |
+         (static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16) |
+         (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Unit u of the interleaved work list -> (is_sparse, tile).
+__device__ __forceinline__ void unit_of(int u, int d_tiles, int s_tiles, bool& sparse, int& tile) {
+  const int paired = min(d_tiles, s_tiles);
+  if (u < 2 * paired) {
+    sparse = (u & 1) != 0;
+    tile = u >> 1;
+  } else {
+    sparse = s_tiles > d_tiles;
+    tile = u - paired;
+  }
+}
+
+template <typename IT> struct IdxVec;
+template <> struct IdxVec<uint16_t> { static constexpr int kVecs = 1; };
+template <> struct IdxVec<int> { static constexpr int kVecs = 2; };
+
+// ND = number of CSR decoder warps (0: dense-only instance).
+template <int ND, typename IT>
+__global__ void __launch_bounds__((kFirstDecodeWarp + ND) * 32, ND > 0 ? 2 : 1)
+tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b_dense,
+                const __grid_constant__ CUtensorMap tma_b_sparse, const Params prm) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int n = prm.n;
+  const uint32_t b_stage_bytes = static_cast<uint32_t>(n) * 256u;
+  const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
+  const int S = prm.num_stages;
+  const uint32_t bar_base = smem_base + S * stage_bytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+  const uint32_t accum_full = bar_base + 8u * (2 * S);
+  const uint32_t accum_empty = bar_base + 8u * (2 * S + 1);
+  const uint32_t tmem_slot = bar_base + 8u * (2 * S + 2);
+  const uint32_t abort_slot = tmem_slot + 4u;
+  // generic pointers to the two 4-byte slots
+  uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_ptr_generic =
+      reinterpret_cast<volatile uint32_t*>(smem_aligned + S * stage_bytes + 8u * (2 * S + 2));
+  volatile int* abort_flag =
+      reinterpret_cast<volatile int*>(smem_aligned + S * stage_bytes + 8u * (2 * S + 2) + 4u);
+  (void)abort_slot;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_units = prm.d_tiles + prm.s_tiles;
+  const int k_blocks = (prm.k + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full_bar(s), 1 + ND);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(accum_full, 1);
+    mbar_init(accum_empty, 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                 "r"(static_cast<uint32_t>(prm.tmem_cols))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_ptr_generic;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b_dense) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b_sparse) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        bool sparse;
+        int tile;
+        unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
+        const bool b_mn = sparse || prm.d_b_mn;
+        const CUtensorMap* tmb = sparse ? &tma_b_sparse : &tma_b_dense;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + s * stage_bytes;
+          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(full_bar(s), b_stage_bytes + (sparse ? 0u : A_STAGE_BYTES));
+          if (!sparse) {
+            tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, tile * BM);
+            tma_load_2d(a_dst + A_ATOM_BYTES, &tma_a, full_bar(s), kb * BK + 64, tile * BM);
+          }
+          if (b_mn) {  // X [K, N]: one [128 k-rows x 64 cols] box per 64 columns
+            for (int j = 0; j < n / 64; ++j)
+              tma_load_2d(b_dst + j * (BK * 128), tmb, full_bar(s), j * 64, kb * BK);
+          } else {  // X^T [N, K]: two [N rows x 64 k] boxes
+            tma_load_2d(b_dst, tmb, full_bar(s), kb * BK, 0);
+            tma_load_2d(b_dst + n * 128, tmb, full_bar(s), kb * BK + 64, 0);
+          }
+        }
+      }
+      if (!ok) {
+        // Drain: give the copies this thread armed a bounded time (~0.2 ms) to land.
+        for (uint32_t i = 0; i < 2048u; ++i) __nanosleep(100);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_k = (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (8u << 24);
+      const uint32_t idesc_mn = idesc_k | (1u << 16);
+      uint32_t it = 0, unit_it = 0;
+      bool ok = true;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
+        bool sparse;
+        int tile;
+        unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
+        const bool b_mn = sparse || prm.d_b_mn;
+        const uint32_t idesc = b_mn ? idesc_mn : idesc_k;
+        if (!mbar_wait(accum_empty, (unit_it & 1u) ^ 1u, abort_flag, prm.status)) { ok = false; break; }
+        tcgen05_fence_after();
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % S;
+          const uint32_t ph = (it / S) & 1u;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t a_base = smem_base + s * stage_bytes;
+          const uint32_t b_base = a_base + A_STAGE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+            const uint64_t adesc =
+                smem_desc(a_base + (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32, 16, 1024);
+            const uint64_t bdesc =
+                b_mn ? smem_desc(b_base + ks * (UMMA_K * 128), BK * 128, 1024)
+                     : smem_desc(b_base + (ks >> 2) * (n * 128) + (ks & 3) * 32, 16, 1024);
+            umma_f16(tmem_base, adesc, bdesc, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+        }
+        if (ok) umma_commit(accum_full);
+      }
+    }
+  } else if (warp < kFirstDecodeWarp) {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t unit_it = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
+      bool sparse;
+      int tile;
+      unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
+      if (!mbar_wait(accum_full, unit_it & 1u, abort_flag, prm.status)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = tile * BM + q * 32 + lane;
+      const int rows = sparse ? prm.s_m : prm.d_m;
+      __half* out = sparse ? prm.s_out : prm.d_out;
+      const long long sm = sparse ? static_cast<long long>(n) : prm.d_stride_m;
+      const long long sn = sparse ? 1ll : prm.d_stride_n;
+      for (int c0 = 0; c0 < n; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 >= n) {  // accumulator fully read: let the next unit's MMAs start
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(accum_empty);
+        }
+        if (row < rows) {
+          if (sn == 1) {
+            uint4* dst = reinterpret_cast<uint4*>(out + row * sm + c0);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 pk;
+              __half2* h = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]),
+                                         __uint_as_float(r[v * 8 + 2 * i + 1]));
+              dst[v] = pk;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              out[row * sm + (c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
+          }
+        }
+      }
+    }
+  } else if (ND > 0) {
+    // ------------------------------------------------------------------ CSR decoders
+    constexpr int kNd = ND > 0 ? ND : 1;
+    constexpr int kRowsPerWarp = BM / kNd;
+    constexpr int kIters = kRowsPerWarp / 4;  // four rows (8 lanes each) per pass
+    static_assert(ND == 0 || (BM % kNd == 0 && kRowsPerWarp % 4 == 0), "decoder split");
+    const int dw = warp - kFirstDecodeWarp;
+    const int grp = lane >> 3, sl = lane & 7;
+    const IT* cols = static_cast<const IT*>(prm.s_cols);
+    const __half* vals = prm.s_values;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      bool sparse;
+      int tile;
+      unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
+      int cur[kIters], rend[kIters];
+      if (sparse) {
+#pragma unroll
+        for (int i = 0; i < kIters; ++i) {
+          const int row = tile * BM + dw * kRowsPerWarp + i * 4 + grp;
+          const bool in = row < prm.s_m;
+          cur[i] = in ? __ldg(prm.s_row_offsets + row) : 0;
+          rend[i] = in ? __ldg(prm.s_row_offsets + row + 1) : 0;
+        }
+      }
+      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        const int s = it % S;
+        const uint32_t ph = (it / S) & 1u;
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status)) { ok = false; break; }
+        if (sparse) {
+          const uint32_t a_base = smem_base + s * stage_bytes;
+          // zero this warp's rows of both atoms (rows are 128 B apart: contiguous)
+          constexpr int kZeroVecs = kRowsPerWarp * 128 / 16 / 32;  // uint4 per lane per atom
+#pragma unroll
+          for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int v = 0; v < kZeroVecs; ++v) {
+              const uint32_t addr =
+                  a_base + a * A_ATOM_BYTES + dw * kRowsPerWarp * 128 + (v * 32 + lane) * 16;
+              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
+            }
+          __syncwarp();
+          const int kbeg = kb * BK, kend = kbeg + BK;
+#pragma unroll
+          for (int i = 0; i < kIters; ++i) {
+            const int row_local = dw * kRowsPerWarp + i * 4 + grp;
+            const uint32_t row_addr = a_base + row_local * 128;
+            const uint32_t swz = static_cast<uint32_t>(row_local & 7) << 4;
+            bool again = cur[i] < rend[i];
+            do {
+              const int base = cur[i] & ~7;
+              const int my = base + sl * 8;
+              int nvalid = 0;
+              if (again && my < rend[i]) {
+                uint32_t vbits[4];
+                int cidx[8];
+                if (my + 8 <= prm.s_nnz) {
+                  const uint4 vv = __ldg(reinterpret_cast<const uint4*>(vals + my));
+                  vbits[0] = vv.x; vbits[1] = vv.y; vbits[2] = vv.z; vbits[3] = vv.w;
+#pragma unroll
+                  for (int q = 0; q < IdxVec<IT>::kVecs; ++q) {
+                    const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cols + my) + q);
+                    const IT* cp = reinterpret_cast<const IT*>(&cv);
+                    constexpr int per = 16 / sizeof(IT);
+#pragma unroll
+                    for (int e = 0; e < per; ++e) cidx[q * per + e] = to_index(cp[e]);
+                  }
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) vbits[e] = 0;
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    cidx[e] = 0x7fffffff;
+                    if (my + e < prm.s_nnz) {
+                      cidx[e] = to_index(__ldg(cols + my + e));
+                      const uint32_t hv = __half_as_ushort(__ldg(vals + my + e));
+                      vbits[e >> 1] |= hv << ((e & 1) * 16);
+                    }
+                  }
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int p = my + e;
+                  const int c = cidx[e];
+                  const bool okp = (p >= cur[i]) & (p < rend[i]) & (c < kend) & (c >= kbeg);
+                  if (okp) {
+                    const uint32_t cl2 = static_cast<uint32_t>(c - kbeg) << 1;  // byte column in [0, 256)
+                    const uint32_t addr = row_addr + ((cl2 & 128u) << 7) + ((cl2 & 127u) ^ swz);
+                    const uint16_t hv = static_cast<uint16_t>(vbits[e >> 1] >> ((e & 1) * 16));
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
+                    ++nvalid;
+                  }
+                }
+              }
+              nvalid += __shfl_xor_sync(0xffffffffu, nvalid, 1);
+              nvalid += __shfl_xor_sync(0xffffffffu, nvalid, 2);
+              nvalid += __shfl_xor_sync(0xffffffffu, nvalid, 4);
+              if (again) {
+                cur[i] += nvalid;
+                // Another pass only when the whole 64-element window was consumed.
+                again = (cur[i] == base + 64) && (cur[i] < rend[i]);
+              }
+            } while (__any_sync(0xffffffffu, again));
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(static_cast<uint32_t>(prm.tmem_cols))
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major fp16 matrix [rows, cols] (cols contiguous); box = [box_rows x 64 cols], 128B swizzle.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return IEX_ERR_DRIVER;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? IEX_OK : IEX_ERR_DRIVER;
+}
+
+int sm_count() {
+  static int sms = [] {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return kNumSMs;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+      return kNumSMs;
+    return v;
+  }();
+  return sms;
+}
+
+int* status_word() {
+  int* p = nullptr;
+  cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_status);
+  return p;
+}
+
+template <int ND, typename IT>
+int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMap& tbs, Params prm,
+                 int stages, int ctas_per_sm, cudaStream_t stream) {
+  prm.num_stages = stages;
+  const size_t smem = 1024 + static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256) +
+                      8 * (2 * stages + 2) + 16;
+  auto kern = tc_units_kernel<ND, IT>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = smem;
+  }
+  const int units = prm.d_tiles + prm.s_tiles;
+  const int grid = units < sm_count() * ctas_per_sm ? units : sm_count() * ctas_per_sm;
+  kern<<<grid, (kFirstDecodeWarp + ND) * 32, smem, stream>>>(ta, tbd, tbs, prm);
+  return launch_status();
+}
+
+int tmem_cols_for(int n) {
+  int c = 32;
+  while (c < n) c <<= 1;
+  return c;
+}
+
+}  // namespace tc
+}  // namespace iex
+
+using namespace iex;
+using namespace iex::tc;
+
+extern "C" int iex_last_device_status(int clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return IEX_ERR_DRIVER;
+  if (clear && v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+extern "C" int iex_linear_f16(int tokens, int in_features, int out_features, const void* input,
+                              const void* weight, void* out, void* stream) {
+  if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
+  if (tokens == 0 || out_features == 0) return IEX_OK;
+  if (!input || !weight || !out) return IEX_ERR_BAD_ARG;
+  if (tokens % 16 != 0 || tokens > 256 || in_features % 8 != 0 || in_features == 0)
+    return IEX_ERR_UNSUPPORTED;
+  if (!aligned16(input) || !aligned16(weight)) return IEX_ERR_UNSUPPORTED;
+  CUtensorMap ta, tb;
+  int st = make_map(&ta, weight, out_features, in_features, BM);
+  if (st) return st;
+  st = make_map(&tb, input, tokens, in_features, tokens);
+  if (st) return st;
+  Params p{};
+  p.d_tiles = (out_features + BM - 1) / BM;
+  p.d_m = out_features;
+  p.d_out = static_cast<__half*>(out);
+  p.d_stride_m = 1;
+  p.d_stride_n = out_features;
+  p.d_b_mn = 0;
+  p.k = in_features;
+  p.n = tokens;
+  p.tmem_cols = tmem_cols_for(tokens);
+  p.status = status_word();
+  const int stage_bytes = A_STAGE_BYTES + tokens * 256;
+  int stages = (220 * 1024) / stage_bytes;
+  stages = stages > 6 ? 6 : stages;
+  if (stages < 2) return IEX_ERR_UNSUPPORTED;
+  return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+
+int sparse_args_ok(int m, int k, int n, int nnz, const int32_t* row_offsets, const void* cols,
+                   const void* values, const void* dense, const void* out, int index_bits) {
+  if (m < 0 || k < 0 || n < 0 || nnz < 0) return IEX_ERR_BAD_ARG;
+  if (index_bits != 16 && index_bits != 32) return IEX_ERR_BAD_ARG;
+  if (!row_offsets || !dense || !out || (nnz > 0 && (!cols || !values))) return IEX_ERR_BAD_ARG;
+  if (n % 64 != 0 || n > 256 || n == 0 || k % 8 != 0 || k == 0) return IEX_ERR_UNSUPPORTED;
+  if (index_bits == 16 && k > 65536) return IEX_ERR_UNSUPPORTED;
+  if (!aligned16(cols) || !aligned16(values) || !aligned16(dense) || !aligned16(out))
+    return IEX_ERR_UNSUPPORTED;
+  return IEX_OK;
+}
+
+}  // namespace
+
+extern "C" int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                               const void* column_indices, int index_bits, const void* values,
+                               const void* dense, void* out, void* stream) {
+  if (m == 0) return IEX_OK;
+  int st = sparse_args_ok(m, k, n, nnz, row_offsets, column_indices, values, dense, out, index_bits);
+  if (st) return st;
+  CUtensorMap tb;
+  st = make_map(&tb, dense, k, n, BK);
+  if (st) return st;
+  Params p{};
+  p.s_tiles = (m + BM - 1) / BM;
+  p.s_m = m;
+  p.s_nnz = nnz;
+  p.s_out = static_cast<__half*>(out);
+  p.s_row_offsets = row_offsets;
+  p.s_cols = column_indices;
+  p.s_values = static_cast<const __half*>(values);
+  p.k = k;
+  p.n = n;
+  p.tmem_cols = tmem_cols_for(n);
+  p.status = status_word();
+  const int stage_bytes = A_STAGE_BYTES + n * 256;
+  int stages = (110 * 1024) / stage_bytes;
+  int ctas = 2;
+  if (stages < 2) { stages = (220 * 1024) / stage_bytes; ctas = 1; }
+  stages = stages > 4 ? 4 : stages;
+  if (stages < 2) return IEX_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (index_bits == 16) return launch_units<8, uint16_t>(tb, tb, tb, p, stages, ctas, s);
+  return launch_units<8, int>(tb, tb, tb, p, stages, ctas, s);
+}
+
+extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, int nnz,
+                                         const int32_t* row_offsets, const void* column_indices,
+                                         int index_bits, const void* values, const void* weight,
+                                         const void* x, void* out_sparse, void* out_dense,
+                                         int dense_out_tokens_major, void* stream) {
+  if (m_dense < 0) return IEX_ERR_BAD_ARG;
+  int st = sparse_args_ok(m_sparse, k, n, nnz, row_offsets, column_indices, values, x, out_sparse,
+                          index_bits);
+  if (st) return st;
+  if (m_dense > 0 && (!weight || !out_dense || !aligned16(weight))) return IEX_ERR_BAD_ARG;
+  if (m_sparse == 0 && m_dense == 0) return IEX_OK;
+  CUtensorMap ta, tb;
+  st = make_map(&tb, x, k, n, BK);
+  if (st) return st;
+  if (m_dense > 0) {
+    st = make_map(&ta, weight, m_dense, k, BM);
+    if (st) return st;
+  } else {
+    ta = tb;
+  }
+  Params p{};
+  p.d_tiles = (m_dense + BM - 1) / BM;
+  p.d_m = m_dense;
+  p.d_out = static_cast<__half*>(out_dense);
+  if (dense_out_tokens_major) { p.d_stride_m = 1; p.d_stride_n = m_dense; }
+  else { p.d_stride_m = n; p.d_stride_n = 1; }
+  p.d_b_mn = 1;
+  p.s_tiles = (m_sparse + BM - 1) / BM;
+  p.s_m = m_sparse;
+  p.s_nnz = nnz;
+  p.s_out = static_cast<__half*>(out_sparse);
+  p.s_row_offsets = row_offsets;
+  p.s_cols = column_indices;
+  p.s_values = static_cast<const __half*>(values);
+  p.k = k;
+  p.n = n;
+  p.tmem_cols = tmem_cols_for(n);
+  p.status = status_word();
+  const int stage_bytes = A_STAGE_BYTES + n * 256;
+  int stages = (110 * 1024) / stage_bytes;
+  int ctas = 2;
+  if (stages < 2) { stages = (220 * 1024) / stage_bytes; ctas = 1; }
+  stages = stages > 4 ? 4 : stages;
+  if (stages < 2) return IEX_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (index_bits == 16) return launch_units<8, uint16_t>(ta, tb, tb, p, stages, ctas, s);
+  return launch_units<8, int>(ta, tb, tb, p, stages, ctas, s);
+}
