@@ -22,8 +22,9 @@
 //
 // Dense units cost almost no instructions (TMA + MMA), sparse units are instruction-bound
 // in the decoders, and both are fed from HBM, so co-resident CTAs working on units of
-// different kinds overlap well: that is the horizontal fusion.  Units of the two kinds
-// alternate in the work list so that neighbouring CTAs (two per SM) hold one of each.
+// different kinds overlap well: that is the horizontal fusion.  One CTA per SM; the work
+// list is ordered so that the long (sparse) units start first and the CTAs that take a
+// second unit are those that began with a short (dense) one.
 //
 // Every wait on an mbarrier is bounded; when a wait gives up the CTA raises a shared
 // abort flag, records IEX_ERR_TIMEOUT in the status word, drains the copies it armed,
@@ -41,7 +42,8 @@ constexpr int UMMA_K = 16;                // K per tcgen05.mma.kind::f16
 constexpr int A_ATOM_BYTES = BM * 128;    // [128 rows x 64 fp16]
 constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
 constexpr int kFirstDecodeWarp = 6;
-constexpr uint32_t kSpinLimit = 1u << 24;  // mbarrier polls before a wait gives up
+constexpr int kDecodeWarps = 16;          // CSR decoder warps of the sparse-capable instance
+constexpr uint32_t kSpinLimit = 1u << 23;  // mbarrier polls (with back-off) before a wait gives up
 
 struct Params {
   // dense branch: out[f * d_stride_m + t * d_stride_n]
@@ -90,15 +92,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "memory");
   return ok;
 }
-// Bounded wait.  Returns false when the wait gave up or another role already aborted.
+// Bounded wait with back-off.  A waiting warp sleeps `sleep_ns` between polls so that it
+// does not take issue slots from the warps doing the work.  Returns false when the wait
+// gave up or another role already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status) {
+                                          int* status, unsigned sleep_ns) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 63u) {
-      if (*abort_flag) return false;
-      __nanosleep(32);
-    }
+    if (i >= 2u) __nanosleep(sleep_ns);
+    if ((i & 63u) == 63u && *abort_flag) return false;
   }
   *abort_flag = 1;
   atomicExch(status, IEX_ERR_TIMEOUT);
@@ -154,25 +156,129 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Unit u of the interleaved work list -> (is_sparse, tile).
-__device__ __forceinline__ void unit_of(int u, int d_tiles, int s_tiles, bool& sparse, int& tile) {
-  const int paired = min(d_tiles, s_tiles);
-  if (u < 2 * paired) {
-    sparse = (u & 1) != 0;
-    tile = u >> 1;
-  } else {
-    sparse = s_tiles > d_tiles;
-    tile = u - paired;
+// Position u of the work list -> (is_sparse, tile).  The list is
+//   dense[0, e)  ++  sparse[0, S)  ++  dense[e, D)      with e = clamp(D + S - grid, 0, D),
+// and CTA c takes positions c, c + grid, ...  Sparse units are the long ones (their cost
+// is decoder instructions), so with at most two waves the CTAs that get a second unit
+// are the ones that started with a (short) dense unit.
+__device__ __forceinline__ void unit_of(int u, int d_tiles, int s_tiles, int grid, bool& sparse,
+                                        int& tile) {
+  int e = d_tiles + s_tiles - grid;
+  e = e < 0 ? 0 : (e > d_tiles ? d_tiles : e);
+  if (u < e) { sparse = false; tile = u; }
+  else if (u < e + s_tiles) { sparse = true; tile = u - e; }
+  else { sparse = false; tile = u - s_tiles; }
+}
+
+// Eight consecutive nonzeros of one row as loaded: raw fp16 bit patterns and indices.
+template <typename IT> struct Window {
+  uint32_t v[4];
+  uint32_t c[8 * sizeof(IT) / 4];
+};
+__device__ __forceinline__ uint32_t window_index(const Window<uint16_t>& w, int e) {
+  return (e & 1) ? (w.c[e >> 1] >> 16) : (w.c[e >> 1] & 0xffffu);
+}
+__device__ __forceinline__ uint32_t window_index(const Window<int>& w, int e) { return w.c[e]; }
+__device__ __forceinline__ void window_kill(Window<uint16_t>& w, int e) {
+  w.c[e >> 1] |= (e & 1) ? 0xffff0000u : 0x0000ffffu;
+}
+__device__ __forceinline__ void window_kill(Window<int>& w, int e) { w.c[e] = 0xffffffffu; }
+
+// Ring staging of the CSR stream.  Every row of the tile has a ring of kRing nonzeros
+// (values and indices) in shared memory, addressed by position modulo kRing, that is
+// kept filled up to kRing positions past the row's cursor with 16-byte cp.async copies
+// ("granules" of 8 nonzeros).  Granules may start before the row or run past its end;
+// what they hold there is masked when a window is read.
+constexpr int kRing = 128;            // nonzeros per row ring
+constexpr int kRingGranules = kRing / 8;
+
+template <typename IT>
+__device__ __forceinline__ void ring_issue(uint32_t vring, uint32_t cring, const __half* __restrict__ vals,
+                                           const IT* __restrict__ cols, int g, int rend, int nnz) {
+  const int p = g * 8;
+  if (p >= rend) return;  // nothing of this row there
+  const uint32_t slot = static_cast<uint32_t>(g) & (kRingGranules - 1);
+  const uint32_t vdst = vring + slot * 16u;
+  const uint32_t cdst = cring + slot * static_cast<uint32_t>(8 * sizeof(IT));
+  if (p + 8 <= nnz) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(vdst), "l"(vals + p) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(cdst), "l"(cols + p) : "memory");
+    if constexpr (sizeof(IT) == 4)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(cdst + 16u), "l"(cols + p + 4)
+                   : "memory");
+  } else {  // last granule of the arrays: element-wise, inside the arrays
+    for (int e = 0; e < 8 && p + e < nnz; ++e) {
+      const uint16_t hv = __half_as_ushort(__ldg(vals + p + e));
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(vdst + 2u * e), "h"(hv) : "memory");
+      if constexpr (sizeof(IT) == 2) {
+        const uint16_t cv = __ldg(cols + p + e);
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(cdst + 2u * e), "h"(cv) : "memory");
+      } else {
+        const uint32_t cv = static_cast<uint32_t>(__ldg(cols + p + e));
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(cdst + 4u * e), "r"(cv) : "memory");
+      }
+    }
   }
 }
 
-template <typename IT> struct IdxVec;
-template <> struct IdxVec<uint16_t> { static constexpr int kVecs = 1; };
-template <> struct IdxVec<int> { static constexpr int kVecs = 2; };
+// Reads nonzeros [my, my + 8) (my a multiple of 8) from the ring.  Positions outside the
+// row [rstart, rend) get an index that no k-block matches, so that the scatter loop needs a
+// single unsigned compare per nonzero.  Positions inside the row but before the cursor
+// hold columns of earlier k-blocks and fail that compare by themselves.
+template <typename IT>
+__device__ __forceinline__ void ring_read(Window<IT>& w, uint32_t vring, uint32_t cring, int my,
+                                          int rstart, int rend) {
+  constexpr int kC = 8 * sizeof(IT) / 4;
+  if (my >= rend) {
+#pragma unroll
+    for (int e = 0; e < kC; ++e) w.c[e] = 0xffffffffu;
+    return;
+  }
+  const uint32_t slot = static_cast<uint32_t>(my >> 3) & (kRingGranules - 1);
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w.v[0]), "=r"(w.v[1]), "=r"(w.v[2]), "=r"(w.v[3])
+               : "r"(vring + slot * 16u));
+#pragma unroll
+  for (int q = 0; q < kC / 4; ++q)
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w.c[4 * q]), "=r"(w.c[4 * q + 1]), "=r"(w.c[4 * q + 2]), "=r"(w.c[4 * q + 3])
+                 : "r"(cring + slot * static_cast<uint32_t>(8 * sizeof(IT)) + 16u * q));
+  if (my + 8 > rend || my < rstart) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (my + e >= rend || my + e < rstart) window_kill(w, e);
+  }
+}
+
+// Writes the window's nonzeros whose column lies in [kbeg, kbeg + 64) into one 64-column
+// atom of the A stage.  row_swz = (address of the row inside the atom) ^ ((row & 7) << 4):
+// XOR-ing the byte column into it applies the 128-byte swizzle.  Returns how many were
+// written.
+template <typename IT>
+__device__ __forceinline__ int scatter_window(const Window<IT>& w, uint32_t kbeg, uint32_t row_swz) {
+  int nvalid = 0;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const uint32_t cl = window_index(w, e) - kbeg;
+    if (cl < 64u) {
+      const uint16_t hv = static_cast<uint16_t>((e & 1) ? (w.v[e >> 1] >> 16) : w.v[e >> 1]);
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(row_swz ^ (cl << 1)), "h"(hv) : "memory");
+      ++nvalid;
+    }
+  }
+  return nvalid;
+}
+// Sum over the 8 lanes of a row group (xor butterfly; all four groups of a warp at once).
+__device__ __forceinline__ int group8_sum(int v, unsigned) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
 
 // ND = number of CSR decoder warps (0: dense-only instance).
 template <int ND, typename IT>
-__global__ void __launch_bounds__((kFirstDecodeWarp + ND) * 32, ND > 0 ? 2 : 1)
+__global__ void __launch_bounds__((kFirstDecodeWarp + ND) * 32, 1)
 tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b_dense,
                 const __grid_constant__ CUtensorMap tma_b_sparse, const Params prm) {
   extern __shared__ uint8_t smem_raw[];
@@ -234,13 +340,13 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         bool sparse;
         int tile;
-        unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
+        unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
         const bool b_mn = sparse || prm.d_b_mn;
         const CUtensorMap* tmb = sparse ? &tma_b_sparse : &tma_b_dense;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
           const uint32_t a_dst = smem_base + s * stage_bytes;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
           mbar_arrive_expect_tx(full_bar(s), b_stage_bytes + (sparse ? 0u : A_STAGE_BYTES));
@@ -272,15 +378,15 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
         bool sparse;
         int tile;
-        unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
+        unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
         const bool b_mn = sparse || prm.d_b_mn;
         const uint32_t idesc = b_mn ? idesc_mn : idesc_k;
-        if (!mbar_wait(accum_empty, (unit_it & 1u) ^ 1u, abort_flag, prm.status)) { ok = false; break; }
+        if (!mbar_wait(accum_empty, (unit_it & 1u) ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
         tcgen05_fence_after();
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status)) { ok = false; break; }
+          if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t a_base = smem_base + s * stage_bytes;
           const uint32_t b_base = a_base + A_STAGE_BYTES;
@@ -306,8 +412,8 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
       bool sparse;
       int tile;
-      unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
-      if (!mbar_wait(accum_full, unit_it & 1u, abort_flag, prm.status)) { ok = false; break; }
+      unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
+      if (!mbar_wait(accum_full, unit_it & 1u, abort_flag, prm.status, 256)) { ok = false; break; }
       tcgen05_fence_after();
       const int row = tile * BM + q * 32 + lane;
       const int rows = sparse ? prm.s_m : prm.d_m;
@@ -346,34 +452,55 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
   } else if (ND > 0) {
     // ------------------------------------------------------------------ CSR decoders
+    // Each warp owns kRowsPerWarp rows of the tile; a group of 8 lanes works on one row,
+    // four rows per pass.  A stage (128 columns) is filled as two 64-column halves, one
+    // swizzle atom each.  A row's nonzeros for one half are a contiguous run that starts
+    // at the row's cursor; the run is read from the row's shared-memory ring as a window
+    // of 64 nonzeros at [base, base+64), base = cursor rounded down to 8 (a second window
+    // when the run is longer).  After each half the ring is topped up to kRing positions
+    // past the new cursor, so global-memory latency is several halves away from use.
     constexpr int kNd = ND > 0 ? ND : 1;
     constexpr int kRowsPerWarp = BM / kNd;
-    constexpr int kIters = kRowsPerWarp / 4;  // four rows (8 lanes each) per pass
+    constexpr int kIters = kRowsPerWarp / 4;
     static_assert(ND == 0 || (BM % kNd == 0 && kRowsPerWarp % 4 == 0), "decoder split");
     const int dw = warp - kFirstDecodeWarp;
     const int grp = lane >> 3, sl = lane & 7;
+    const unsigned gmask = 0xffu << (grp * 8);
     const IT* cols = static_cast<const IT*>(prm.s_cols);
     const __half* vals = prm.s_values;
+    const int nnz = prm.s_nnz;
+    const uint32_t ring_base = bar_base + 8u * (2 * S + 2) + 16u;  // 16-byte aligned
     uint32_t it = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
       bool sparse;
       int tile;
-      unit_of(u, prm.d_tiles, prm.s_tiles, sparse, tile);
-      int cur[kIters], rend[kIters];
+      unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
+      int cur[kIters], rend[kIters], rstart[kIters], filled[kIters];
+      uint32_t vring[kIters], cring[kIters];
       if (sparse) {
 #pragma unroll
         for (int i = 0; i < kIters; ++i) {
-          const int row = tile * BM + dw * kRowsPerWarp + i * 4 + grp;
+          const int row_local = dw * kRowsPerWarp + i * 4 + grp;
+          const int row = tile * BM + row_local;
           const bool in = row < prm.s_m;
-          cur[i] = in ? __ldg(prm.s_row_offsets + row) : 0;
+          rstart[i] = in ? __ldg(prm.s_row_offsets + row) : 0;
           rend[i] = in ? __ldg(prm.s_row_offsets + row + 1) : 0;
+          cur[i] = rstart[i];
+          vring[i] = ring_base + row_local * (kRing * 2u);
+          cring[i] = ring_base + BM * (kRing * 2u) + row_local * (kRing * static_cast<uint32_t>(sizeof(IT)));
+          const int g0 = rstart[i] >> 3;
+          ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + sl, rend[i], nnz);
+          ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + 8 + sl, rend[i], nnz);
+          filled[i] = g0 + kRingGranules;
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");  // so that wait_group 1 covers the fill
       }
       for (int kb = 0; kb < k_blocks; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status)) { ok = false; break; }
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 32)) { ok = false; break; }
         if (sparse) {
           const uint32_t a_base = smem_base + s * stage_bytes;
           // zero this warp's rows of both atoms (rows are 128 B apart: contiguous)
@@ -386,73 +513,64 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                   a_base + a * A_ATOM_BYTES + dw * kRowsPerWarp * 128 + (v * 32 + lane) * 16;
               asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
             }
-          __syncwarp();
-          const int kbeg = kb * BK, kend = kbeg + BK;
 #pragma unroll
-          for (int i = 0; i < kIters; ++i) {
-            const int row_local = dw * kRowsPerWarp + i * 4 + grp;
-            const uint32_t row_addr = a_base + row_local * 128;
-            const uint32_t swz = static_cast<uint32_t>(row_local & 7) << 4;
-            bool again = cur[i] < rend[i];
-            do {
-              const int base = cur[i] & ~7;
-              const int my = base + sl * 8;
-              int nvalid = 0;
-              if (again && my < rend[i]) {
-                uint32_t vbits[4];
-                int cidx[8];
-                if (my + 8 <= prm.s_nnz) {
-                  const uint4 vv = __ldg(reinterpret_cast<const uint4*>(vals + my));
-                  vbits[0] = vv.x; vbits[1] = vv.y; vbits[2] = vv.z; vbits[3] = vv.w;
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t kbeg = static_cast<uint32_t>(kb * BK + h * 64);
+            // everything but the newest top-up has landed; make it visible to the warp
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+            __syncwarp();
+            Window<IT> w[kIters];
+            int base[kIters], nv[kIters];
+            uint32_t row_swz[kIters];
+            bool more[kIters];
+            bool any_more = false;
 #pragma unroll
-                  for (int q = 0; q < IdxVec<IT>::kVecs; ++q) {
-                    const uint4 cv = __ldg(reinterpret_cast<const uint4*>(cols + my) + q);
-                    const IT* cp = reinterpret_cast<const IT*>(&cv);
-                    constexpr int per = 16 / sizeof(IT);
+            for (int i = 0; i < kIters; ++i) {
+              const int row_local = dw * kRowsPerWarp + i * 4 + grp;
+              row_swz[i] = (a_base + h * A_ATOM_BYTES + row_local * 128) ^
+                           (static_cast<uint32_t>(row_local & 7) << 4);
+              base[i] = cur[i] & ~7;
+              ring_read<IT>(w[i], vring[i], cring[i], base[i] + sl * 8, rstart[i], rend[i]);
+            }
 #pragma unroll
-                    for (int e = 0; e < per; ++e) cidx[q * per + e] = to_index(cp[e]);
-                  }
-                } else {
+            for (int i = 0; i < kIters; ++i) nv[i] = scatter_window<IT>(w[i], kbeg, row_swz[i]);
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) vbits[e] = 0;
+            for (int i = 0; i < kIters; ++i) {
+              cur[i] += group8_sum(nv[i], gmask);
+              more[i] = (cur[i] == base[i] + 64) && (cur[i] < rend[i]);
+              any_more |= more[i];
+            }
+            if (__any_sync(0xffffffffu, any_more)) {  // some run is longer than its window
+              asm volatile("cp.async.wait_group 0;" ::: "memory");
+              __syncwarp();
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) {
-                    cidx[e] = 0x7fffffff;
-                    if (my + e < prm.s_nnz) {
-                      cidx[e] = to_index(__ldg(cols + my + e));
-                      const uint32_t hv = __half_as_ushort(__ldg(vals + my + e));
-                      vbits[e >> 1] |= hv << ((e & 1) * 16);
-                    }
-                  }
+              for (int i = 0; i < kIters; ++i) {
+                int n2 = 0;
+                if (more[i]) {
+                  ring_read<IT>(w[i], vring[i], cring[i], base[i] + 64 + sl * 8, rstart[i], rend[i]);
+                  n2 = scatter_window<IT>(w[i], kbeg, row_swz[i]);
                 }
+                cur[i] += group8_sum(n2, gmask);
+              }
+            }
+            // top the rings up to kRing positions past the new window bases
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int p = my + e;
-                  const int c = cidx[e];
-                  const bool okp = (p >= cur[i]) & (p < rend[i]) & (c < kend) & (c >= kbeg);
-                  if (okp) {
-                    const uint32_t cl2 = static_cast<uint32_t>(c - kbeg) << 1;  // byte column in [0, 256)
-                    const uint32_t addr = row_addr + ((cl2 & 128u) << 7) + ((cl2 & 127u) ^ swz);
-                    const uint16_t hv = static_cast<uint16_t>(vbits[e >> 1] >> ((e & 1) * 16));
-                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
-                    ++nvalid;
-                  }
-                }
-              }
-              nvalid += __shfl_xor_sync(0xffffffffu, nvalid, 1);
-              nvalid += __shfl_xor_sync(0xffffffffu, nvalid, 2);
-              nvalid += __shfl_xor_sync(0xffffffffu, nvalid, 4);
-              if (again) {
-                cur[i] += nvalid;
-                // Another pass only when the whole 64-element window was consumed.
-                again = (cur[i] == base + 64) && (cur[i] < rend[i]);
-              }
-            } while (__any_sync(0xffffffffu, again));
+            for (int i = 0; i < kIters; ++i) {
+              const int limit = (cur[i] >> 3) + kRingGranules;
+              const int g = filled[i] + sl;
+              if (g < limit) ring_issue<IT>(vring[i], cring[i], vals, cols, g, rend[i], nnz);
+              filled[i] = limit > filled[i] ? limit : filled[i];
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
+      }
+      if (sparse) {  // nothing of this unit may still be landing when the rings are reused
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
       }
     }
   }
@@ -523,8 +641,9 @@ template <int ND, typename IT>
 int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMap& tbs, Params prm,
                  int stages, int ctas_per_sm, cudaStream_t stream) {
   prm.num_stages = stages;
+  const size_t ring = ND > 0 ? static_cast<size_t>(BM) * kRing * (2 + sizeof(IT)) : 0;
   const size_t smem = 1024 + static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256) +
-                      8 * (2 * stages + 2) + 16;
+                      8 * (2 * stages + 2) + 32 + ring;
   auto kern = tc_units_kernel<ND, IT>;
   static size_t configured = 0;
   if (smem > configured) {
@@ -594,13 +713,21 @@ extern "C" int iex_linear_f16(int tokens, int in_features, int out_features, con
 
 namespace {
 
+// Stages that fit beside the CSR rings in one CTA's shared memory (one CTA per SM).
+int sparse_stages(int n, int index_bits) {
+  const int ring = BM * kRing * (2 + index_bits / 8);
+  const int stage_bytes = A_STAGE_BYTES + n * 256;
+  int stages = (224 * 1024 - ring) / stage_bytes;
+  return stages > 4 ? 4 : stages;
+}
+
 int sparse_args_ok(int m, int k, int n, int nnz, const int32_t* row_offsets, const void* cols,
                    const void* values, const void* dense, const void* out, int index_bits) {
   if (m < 0 || k < 0 || n < 0 || nnz < 0) return IEX_ERR_BAD_ARG;
   if (index_bits != 16 && index_bits != 32) return IEX_ERR_BAD_ARG;
   if (!row_offsets || !dense || !out || (nnz > 0 && (!cols || !values))) return IEX_ERR_BAD_ARG;
   if (n % 64 != 0 || n > 256 || n == 0 || k % 8 != 0 || k == 0) return IEX_ERR_UNSUPPORTED;
-  if (index_bits == 16 && k > 65536) return IEX_ERR_UNSUPPORTED;
+  if (index_bits == 16 && k > 65280) return IEX_ERR_UNSUPPORTED;  // 0xffff marks padding
   if (!aligned16(cols) || !aligned16(values) || !aligned16(dense) || !aligned16(out))
     return IEX_ERR_UNSUPPORTED;
   return IEX_OK;
@@ -629,15 +756,11 @@ extern "C" int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_
   p.n = n;
   p.tmem_cols = tmem_cols_for(n);
   p.status = status_word();
-  const int stage_bytes = A_STAGE_BYTES + n * 256;
-  int stages = (110 * 1024) / stage_bytes;
-  int ctas = 2;
-  if (stages < 2) { stages = (220 * 1024) / stage_bytes; ctas = 1; }
-  stages = stages > 4 ? 4 : stages;
+  const int stages = sparse_stages(n, index_bits);
   if (stages < 2) return IEX_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (index_bits == 16) return launch_units<8, uint16_t>(tb, tb, tb, p, stages, ctas, s);
-  return launch_units<8, int>(tb, tb, tb, p, stages, ctas, s);
+  if (index_bits == 16) return launch_units<kDecodeWarps, uint16_t>(tb, tb, tb, p, stages, 1, s);
+  return launch_units<kDecodeWarps, int>(tb, tb, tb, p, stages, 1, s);
 }
 
 extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, int nnz,
@@ -678,13 +801,9 @@ extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n
   p.n = n;
   p.tmem_cols = tmem_cols_for(n);
   p.status = status_word();
-  const int stage_bytes = A_STAGE_BYTES + n * 256;
-  int stages = (110 * 1024) / stage_bytes;
-  int ctas = 2;
-  if (stages < 2) { stages = (220 * 1024) / stage_bytes; ctas = 1; }
-  stages = stages > 4 ? 4 : stages;
+  const int stages = sparse_stages(n, index_bits);
   if (stages < 2) return IEX_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (index_bits == 16) return launch_units<8, uint16_t>(ta, tb, tb, p, stages, ctas, s);
-  return launch_units<8, int>(ta, tb, tb, p, stages, ctas, s);
+  if (index_bits == 16) return launch_units<kDecodeWarps, uint16_t>(ta, tb, tb, p, stages, 1, s);
+  return launch_units<kDecodeWarps, int>(ta, tb, tb, p, stages, 1, s);
 }
