@@ -768,9 +768,16 @@ extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n
                                          int index_bits, const void* values, const void* weight,
                                          const void* x, void* out_sparse, void* out_dense,
                                          int dense_out_tokens_major, void* stream) {
-  if (m_dense < 0) return IEX_ERR_BAD_ARG;
-  int st = sparse_args_ok(m_sparse, k, n, nnz, row_offsets, column_indices, values, x, out_sparse,
-                          index_bits);
+  if (m_dense < 0 || m_sparse < 0) return IEX_ERR_BAD_ARG;
+  int st;
+  if (m_sparse > 0) {
+    st = sparse_args_ok(m_sparse, k, n, nnz, row_offsets, column_indices, values, x, out_sparse,
+                        index_bits);
+  } else {  // dense branch alone: same limits on k, n and x
+    static const int32_t kNoRows[1] = {0};
+    st = sparse_args_ok(0, k, n, 0, kNoRows, nullptr, nullptr, x, x, 16);
+    index_bits = 16;
+  }
   if (st) return st;
   if (m_dense > 0 && (!weight || !out_dense || !aligned16(weight))) return IEX_ERR_BAD_ARG;
   if (m_sparse == 0 && m_dense == 0) return IEX_OK;

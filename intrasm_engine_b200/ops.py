@@ -12,8 +12,9 @@ Deliberate differences from the reference, all supersets:
     it takes int16 or int32 column indices.
   * The atomic variants zero their output before accumulating; the reference accumulates
     onto an uninitialised ``at::empty`` tensor (sputnik_kernels.cpp:91, :21-24).
-  * ``linear_fp16`` and ``fused_spmm_linear_fp16`` are new ops for the dense branch and the
-    fused sparse||dense layer; the reference has no kernel of its own for either.
+  * ``linear_fp16``, ``spmm_tc_half`` and ``fused_spmm_linear_half`` are new ops for the dense
+    branch, the tensor-core SpMM and the fused sparse||dense layer; the reference has no
+    kernel of its own for any of them.
 """
 from __future__ import annotations
 
@@ -134,6 +135,82 @@ def sddmm_sputnik_atomic_upd_weight(a, b, row_indices, row_offsets, column_indic
     return out
 
 
+def linear_fp16(input, weight):
+    """Dense branch on tensor cores: ``input @ weight.T`` (fp16 in, fp32 accumulate, fp16 out).
+
+    ``input`` ``[tokens, in_features]``, ``weight`` ``[out_features, in_features]`` — the
+    computation of MyLinear.forward (layers_and_funcs/torch.py:17).  tokens must be a multiple
+    of 16 and at most 256, in_features a multiple of 8.
+    """
+    _check(input.dim() == 2 and weight.dim() == 2, "input and weight must be 2-D")
+    _check(input.size(1) == weight.size(1), "input and weight disagree on in_features")
+    _common_checks({"input": input, "weight": weight})
+    _check(input.dtype == torch.float16 and weight.dtype == torch.float16, "input and weight must be float16")
+    tokens, cin = input.shape
+    cout = weight.size(0)
+    with torch.cuda.device(input.device):
+        out = torch.empty((tokens, cout), dtype=input.dtype, device=input.device)
+        _lib.call("iex_linear_f16", tokens, cin, cout, input.data_ptr(), weight.data_ptr(),
+                  out.data_ptr(), _stream_ptr(input.device))
+    return out
+
+
+def _tc_sparse_checks(x, row_offsets, values, column_indices, m):
+    _check(x.dim() == 2, "x must be [k, n]")
+    _check(values.dim() == 1 and values.size(0) == column_indices.size(0),
+           "values and column_indices must be 1-D with nnz entries")
+    _check(row_offsets.dim() == 1 and row_offsets.size(0) == m + 1, "row_offsets must have m + 1 entries")
+    _common_checks({"x": x, "row_offsets": row_offsets, "values": values, "column_indices": column_indices})
+    _check(x.dtype == torch.float16 and values.dtype == torch.float16, "x and values must be float16")
+    _check(row_offsets.dtype == torch.int32, "row_offsets must be int32")
+    _check(column_indices.dtype in (torch.int16, torch.int32), "column_indices must be int16 or int32")
+    return 16 if column_indices.dtype == torch.int16 else 32
+
+
+def spmm_tc_half(x, row_offsets, values, column_indices, m):
+    """CSR SpMM on tensor cores: ``A @ x`` with A ``[m, k]`` in CSR and x ``[k, n]`` fp16.
+
+    Column indices must ascend inside each row (what every CSR converter produces); rows
+    are taken in natural order, so there is no ``row_indices`` argument.  n must be 64 or
+    128 and k a multiple of 8.  Returns ``[m, n]``.
+    """
+    m = int(m)
+    bits = _tc_sparse_checks(x, row_offsets, values, column_indices, m)
+    k, n = x.shape
+    with torch.cuda.device(x.device):
+        out = torch.empty((m, n), dtype=x.dtype, device=x.device)
+        _lib.call("iex_spmm_f16_tc", m, k, n, column_indices.size(0), row_offsets.data_ptr(),
+                  column_indices.data_ptr(), bits, values.data_ptr(), x.data_ptr(), out.data_ptr(),
+                  _stream_ptr(x.device))
+    return out
+
+
+def fused_spmm_linear_half(x, row_offsets, values, column_indices, m, weight):
+    """Fused sparse || dense layer in ONE launch, both branches reading ``x`` ``[k, n]``:
+
+        out_sparse = A_csr @ x            ``[m, n]``
+        out_dense  = (weight @ x).T       ``[n, out_features]``   (MyLinear's layout)
+
+    The reference has no kernel for this; its pair function runs the two library calls
+    on two captured streams (tests/test_interleaving.py:434-476).
+    """
+    m = int(m)
+    bits = _tc_sparse_checks(x, row_offsets, values, column_indices, m)
+    _check(weight.dim() == 2 and weight.size(1) == x.size(0), "weight must be [out_features, k]")
+    _common_checks({"x": x, "weight": weight})
+    _check(weight.dtype == torch.float16, "weight must be float16")
+    k, n = x.shape
+    md = weight.size(0)
+    with torch.cuda.device(x.device):
+        out_s = torch.empty((m, n), dtype=x.dtype, device=x.device)
+        out_d = torch.empty((n, md), dtype=x.dtype, device=x.device)
+        _lib.call("iex_fused_spmm_linear_f16", m, md, k, n, column_indices.size(0),
+                  row_offsets.data_ptr(), column_indices.data_ptr(), bits, values.data_ptr(),
+                  weight.data_ptr(), x.data_ptr(), out_s.data_ptr(), out_d.data_ptr(), 1,
+                  _stream_ptr(x.device))
+    return out_s, out_d
+
+
 _SPMM_SCHEMA = ("(Tensor b, Tensor row_indices, Tensor values, Tensor row_offsets, "
                 "Tensor column_indices, int m) -> Tensor")
 _DEF.define("spmm_sputnik_reuse_weight" + _SPMM_SCHEMA)
@@ -141,6 +218,13 @@ _DEF.define("spmm_sputnik_atomic" + _SPMM_SCHEMA)
 _DEF.define("spmm_sputnik_reuse_weight_half" + _SPMM_SCHEMA)
 _DEF.define("sddmm_sputnik_atomic_upd_weight(Tensor a, Tensor b, Tensor row_indices, "
             "Tensor row_offsets, Tensor column_indices) -> Tensor")
+_DEF.define("linear_fp16(Tensor input, Tensor weight) -> Tensor")
+_DEF.define("spmm_tc_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, int m) -> Tensor")
+_DEF.define("fused_spmm_linear_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, "
+            "int m, Tensor weight) -> (Tensor, Tensor)")
+_DEF.impl("linear_fp16", linear_fp16, "CUDA")
+_DEF.impl("spmm_tc_half", spmm_tc_half, "CUDA")
+_DEF.impl("fused_spmm_linear_half", fused_spmm_linear_half, "CUDA")
 _DEF.impl("spmm_sputnik_reuse_weight", spmm_sputnik_reuse_weight, "CUDA")
 _DEF.impl("spmm_sputnik_atomic", spmm_sputnik_atomic, "CUDA")
 _DEF.impl("spmm_sputnik_reuse_weight_half", spmm_sputnik_reuse_weight_half, "CUDA")

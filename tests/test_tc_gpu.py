@@ -1,0 +1,184 @@
+"""GPU parity: the tensor-core (tcgen05) entry points through the C ABI.
+
+fp16 inputs, fp32 accumulation inside the tensor core, fp16 output.  The accumulation
+order is the hardware's, so the bar is the task's fp16 tolerance: 1e-2 relative to the fp32
+result (plus 1e-2 of the tensor's max magnitude for cancelled sums); in practice the error
+is the final fp16 rounding (about 5e-4).  The fp32 reference is the CPU oracle / torch CPU
+path on the same inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from intrasm_engine_b200 import _lib, synthetic as syn
+from . import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-2
+
+
+def _linear(x, w):
+    tokens, cin = x.shape
+    out = torch.empty((tokens, w.shape[0]), dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_linear_f16", tokens, cin, w.shape[0], x.data_ptr(), w.data_ptr(), out.data_ptr(),
+              G.stream_ptr())
+    return out
+
+
+def _spmm_tc(a, dense):
+    k, n = dense.shape
+    out = torch.empty((a.m, n), dtype=torch.float16, device=G.DEV)
+    bits = 16 if a.column_indices.dtype == torch.int16 else 32
+    _lib.call("iex_spmm_f16_tc", a.m, k, n, a.nnz, a.row_offsets.data_ptr(), G.ptr(a.column_indices), bits,
+              G.ptr(a.values), dense.data_ptr(), out.data_ptr(), G.stream_ptr())
+    return out
+
+
+def _fused(a, w, x):
+    k, n = x.shape
+    out_s = torch.empty((a.m, n), dtype=torch.float16, device=G.DEV)
+    out_d = torch.empty((n, w.shape[0]), dtype=torch.float16, device=G.DEV)
+    bits = 16 if a.column_indices.dtype == torch.int16 else 32
+    _lib.call("iex_fused_spmm_linear_f16", a.m, w.shape[0], k, n, a.nnz, a.row_offsets.data_ptr(),
+              G.ptr(a.column_indices), bits, G.ptr(a.values), w.data_ptr(), x.data_ptr(), out_s.data_ptr(),
+              out_d.data_ptr(), 1, G.stream_ptr())
+    return out_s, out_d
+
+
+def _status_clean():
+    torch.cuda.synchronize()
+    assert _lib.lib.iex_last_device_status(1) == 0
+
+
+def test_linear_golden(oracle, golden_dir):
+    g = np.load(golden_dir + "/linear_f16_16x64x48.npz")
+    got = _linear(G.dev(g["input"]), G.dev(g["weight"])).cpu().numpy()
+    assert G.close(got, g["out"], RTOL, RTOL)
+    assert G.close(got, oracle.linear(g["input"], g["weight"]), RTOL, RTOL)
+    _status_clean()
+
+
+@pytest.mark.parametrize("tokens,cin,cout", [(16, 8, 8), (16, 64, 128), (64, 128, 128), (64, 256, 384),
+                                             (32, 520, 200), (128, 1024, 1000), (256, 328, 640),
+                                             (48, 4096, 256), (64, 4096, 12288)])
+def test_linear_shapes(tokens, cin, cout):
+    rng = np.random.default_rng(tokens + cin + cout)
+    x = rng.standard_normal((tokens, cin)).astype(np.float16)
+    w = (rng.standard_normal((cout, cin)) * 0.05).astype(np.float16)
+    got = _linear(G.dev(x), G.dev(w)).cpu().numpy()
+    ref = x.astype(np.float32) @ w.astype(np.float32).T
+    assert G.close(got, ref, RTOL, RTOL), G.max_violation(got, ref, RTOL, RTOL)
+    assert G.max_violation(got, ref, 1e-3, 1e-3) < 1.0  # fp16 rounding only
+    _status_clean()
+
+
+def test_linear_rejects_unsupported():
+    x = torch.zeros((20, 64), dtype=torch.float16, device=G.DEV)
+    w = torch.zeros((64, 64), dtype=torch.float16, device=G.DEV)
+    with pytest.raises(_lib.IexError) as e:
+        _linear(x, w)  # tokens not a multiple of 16
+    assert e.value.status == -2
+    x = torch.zeros((512, 64), dtype=torch.float16, device=G.DEV)
+    with pytest.raises(_lib.IexError):
+        _linear(x, w)  # tokens > 256
+
+
+@pytest.mark.parametrize("m,k,n,density,idx", [
+    (128, 128, 64, 0.5, np.int16), (1, 8, 64, 1.0, np.int16), (130, 264, 64, 0.5, np.int32),
+    (300, 1024, 64, 0.3, np.int16), (256, 512, 128, 0.1, np.int32), (256, 512, 128, 0.9, np.int16),
+    (64, 2048, 64, 1.0, np.int16), (200, 640, 64, 0.0, np.int16), (512, 4096, 64, 0.02, np.int16),
+    (1024, 2048, 128, 0.5, np.int16),
+])
+def test_spmm_tc_shapes(oracle, m, k, n, density, idx):
+    rng = np.random.default_rng(m * 7 + k + n)
+    mask = rng.random((m, k)) < density
+    if density > 0:
+        mask[0] = True        # a fully dense row exercises the long-run path
+        mask[m // 2] = False  # and an empty one
+    a = syn.csr_from_mask(mask, rng=rng, std=0.05, dtype=np.float16, index_dtype=idx)
+    b = rng.standard_normal((k, n)).astype(np.float16)
+    got = _spmm_tc(G.DevCSR(a), G.dev(b)).cpu().numpy()
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, m)[0]
+    assert G.close(got, ref, RTOL, RTOL), G.max_violation(got, ref, RTOL, RTOL)
+    assert G.max_violation(got, ref, 1e-3, 1e-3) < 1.0
+    _status_clean()
+
+
+def test_spmm_tc_matches_cuda_core_kernel():
+    """Two independent kernels (CUDA cores, bit-exact with the oracle; tensor cores) agree."""
+    a, b = syn.pruned_sweep_case(7, 2048, 512, 0.7, 128)
+    da = G.DevCSR(a)
+    simt = G.spmm_f16(da, G.dev(b)[None])[0].float()
+    tc = _spmm_tc(da, G.dev(b)).float()
+    assert torch.allclose(simt, tc, rtol=2e-3, atol=2e-3 * float(simt.abs().max()))
+    _status_clean()
+
+
+def test_spmm_tc_rejects_unsupported():
+    a, b = syn.pruned_sweep_case(1, 64, 128, 0.5, 64)
+    da = G.DevCSR(a)
+    with pytest.raises(_lib.IexError):
+        _spmm_tc(da, G.dev(b[:, :48].copy()))  # n not a multiple of 64
+    with pytest.raises(_lib.IexError):
+        _lib.call("iex_spmm_f16_tc", 64, 128, 64, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
+                  8, da.values.data_ptr(), G.dev(b).data_ptr(), G.dev(b).data_ptr(), None)
+
+
+@pytest.mark.parametrize("ms,md,k,n", [(256, 256, 512, 64), (100, 300, 264, 64), (384, 128, 1024, 128),
+                                        (128, 0, 256, 64), (0, 256, 256, 64)])
+def test_fused_small(oracle, ms, md, k, n):
+    a, w, x = syn.fused_layer_case(ms + md, max(ms, 1), k, n, max(md, 1))
+    if ms == 0:
+        a = syn.csr_from_mask(np.zeros((0, k), bool), rng=np.random.default_rng(0), dtype=np.float16,
+                              index_dtype=np.int16)
+    if md == 0:
+        w = w[:0]
+    da = G.DevCSR(a)
+    dw = G.dev(w) if md else torch.zeros((0, k), dtype=torch.float16, device=G.DEV)
+    out_s, out_d = _fused(da, dw, G.dev(x))
+    if ms:
+        ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, ms)[0]
+        assert G.close(out_s.cpu().numpy(), ref_s, RTOL, RTOL)
+    if md:
+        ref_d = x.astype(np.float32).T @ w.astype(np.float32).T
+        assert G.close(out_d.cpu().numpy(), ref_d, RTOL, RTOL)
+    _status_clean()
+
+
+def test_fused_cfg4_full_size(oracle):
+    """BASELINE config 4: W_up 11008x4096 CSR at 50 % times X 4096x64, fused with W_qkv 12288x4096."""
+    a, w, x = syn.fused_layer_case(0)
+    da = G.DevCSR(a)
+    out_s, out_d = _fused(da, G.dev(w), G.dev(x))
+    ref_s = oracle.torch_spmm(a.row_offsets, a.column_indices, a.values, x, 11008)
+    ref_d = oracle.torch_linear(x.T, w)
+    gs, gd = out_s.cpu().numpy(), out_d.cpu().numpy()
+    assert G.close(gs, ref_s, RTOL, RTOL), G.max_violation(gs, ref_s, RTOL, RTOL)
+    assert G.close(gd, ref_d, RTOL, RTOL), G.max_violation(gd, ref_d, RTOL, RTOL)
+    # the fused launch and the two separate launches give identical bits
+    sep_s = _spmm_tc(da, G.dev(x))
+    sep_d = _linear(G.dev(np.ascontiguousarray(x.T)), G.dev(w))
+    assert torch.equal(sep_s, out_s)
+    assert torch.allclose(sep_d.float(), out_d.float(), rtol=2e-3, atol=2e-3)
+    # int32 indices: same values
+    da.column_indices = da.column_indices.to(torch.int32)
+    out_s32, _ = _fused(da, G.dev(w), G.dev(x))
+    assert torch.equal(out_s32, out_s)
+    _status_clean()
+
+
+def test_torch_ops_tc(oracle):
+    import intrasm_engine_b200  # noqa: F401
+    ops = torch.ops.iex_ops
+    a, w, x = syn.fused_layer_case(5, 256, 512, 64, 384)
+    da = G.DevCSR(a)
+    xs, ws = G.dev(x), G.dev(w)
+    out_s, out_d = ops.fused_spmm_linear_half(xs, da.row_offsets, da.values, da.column_indices, 256, ws)
+    assert torch.equal(out_s, ops.spmm_tc_half(xs, da.row_offsets, da.values, da.column_indices, 256))
+    lin = ops.linear_fp16(xs.t().contiguous(), ws)
+    assert lin.shape == out_d.shape
+    assert torch.allclose(lin.float(), out_d.float(), rtol=2e-3, atol=2e-3)
+    ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, 256)[0]
+    assert G.close(out_s.cpu().numpy(), ref_s, RTOL, RTOL)
+    with pytest.raises(RuntimeError):
+        ops.linear_fp16(xs.t().contiguous().float(), ws)
