@@ -141,6 +141,42 @@ IEX_API int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, i
  * Synchronises the device.  clear != 0 resets the word. */
 IEX_API int iex_last_device_status(int clear);
 
+/* ------------------------------------------------------------------------------------
+ * CUDA-graph constructor: one graph assembled from work enqueued on several registered
+ * streams, so that independent chains can be co-scheduled by the hardware.
+ *
+ * Replaces the pybind classes CUDAExperimentalGraphConstructor / CudaGraphWrapper
+ * (intrasm_engine/pytorch/csrc/extensions/pybind.cu:529-615) and the native code under
+ * them (intrasm_engine/common/include/helper_CUDAGraphConstructor.cu.h:106-166, :268-486;
+ * helper_cuda_graph.cu.h:34-62).  Handles are opaque pointers; streams and events are
+ * cudaStream_t / cudaEvent_t values, as the reference passes them (pybind.cu:367-399).
+ * Host-only calls; a constructor must be used from one thread at a time.
+ *   create / destroy                      CudaGraphWrapper ctor / dtor
+ *   register_stream                       register_stream          (pybind.cu:553)
+ *   add_event_record_node                 add_event_record_node
+ *   add_stream_wait_event_node            add_stream_wait_event_node
+ *   join                                  join
+ *   capture_begin / capture_end           notify_before / notify_after_invoking_library_call
+ *   instantiate / launch / exec_destroy   instantiate_graph_exec / execute_graph / destroy_graph_exec
+ *   add_child / combine                   add_graph_as_child_node / combine_graphs
+ *   dump / node_count                     dump_graph / print_graph
+ * ------------------------------------------------------------------------------------ */
+IEX_API void* iex_graph_create(void);
+IEX_API int iex_graph_destroy(void* graph);
+IEX_API int iex_graph_register_stream(void* graph, void* stream);
+IEX_API int iex_graph_add_event_record_node(void* graph, void* event, void* stream);
+IEX_API int iex_graph_add_stream_wait_event_node(void* graph, void* stream, void* event);
+IEX_API int iex_graph_join(void* graph, void* const* streams, int count, void* dst_stream);
+IEX_API int iex_graph_capture_begin(void* graph, void* stream);
+IEX_API int iex_graph_capture_end(void* graph, void* stream);
+IEX_API int iex_graph_instantiate(void* graph);
+IEX_API int iex_graph_launch(void* graph, void* stream);
+IEX_API int iex_graph_exec_destroy(void* graph);
+IEX_API int iex_graph_node_count(void* graph, long long* nodes, long long* edges);
+IEX_API int iex_graph_dump(void* graph, const char* path);
+IEX_API int iex_graph_add_child(void* graph, void* child);
+IEX_API void* iex_graph_combine(void* const* graphs, int count);
+
 #ifdef __cplusplus
 }
 #endif

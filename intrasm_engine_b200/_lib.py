@@ -42,6 +42,22 @@ SIGNATURES = {
     "iex_fused_spmm_linear_f16": (c_int, [c_int, c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int,
                                           c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
+    # graph constructor (opaque handle first)
+    "iex_graph_create": (c_ptr, []),
+    "iex_graph_destroy": (c_int, [c_ptr]),
+    "iex_graph_register_stream": (c_int, [c_ptr, c_ptr]),
+    "iex_graph_add_event_record_node": (c_int, [c_ptr, c_ptr, c_ptr]),
+    "iex_graph_add_stream_wait_event_node": (c_int, [c_ptr, c_ptr, c_ptr]),
+    "iex_graph_join": (c_int, [c_ptr, ctypes.POINTER(c_ptr), c_int, c_ptr]),
+    "iex_graph_capture_begin": (c_int, [c_ptr, c_ptr]),
+    "iex_graph_capture_end": (c_int, [c_ptr, c_ptr]),
+    "iex_graph_instantiate": (c_int, [c_ptr]),
+    "iex_graph_launch": (c_int, [c_ptr, c_ptr]),
+    "iex_graph_exec_destroy": (c_int, [c_ptr]),
+    "iex_graph_node_count": (c_int, [c_ptr, ctypes.POINTER(c_ll), ctypes.POINTER(c_ll)]),
+    "iex_graph_dump": (c_int, [c_ptr, ctypes.c_char_p]),
+    "iex_graph_add_child": (c_int, [c_ptr, c_ptr]),
+    "iex_graph_combine": (c_ptr, [ctypes.POINTER(c_ptr), c_int]),
 }
 
 
