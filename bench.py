@@ -238,15 +238,17 @@ def run_ours(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # clocks are sampled from before the warm-up to after the end-to-end region, so that
+    # even a short timed region has samples under load
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         sddmm_all()
         spmm_all()
     barrier()
 
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     barrier()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
@@ -259,7 +261,6 @@ def run_ours(args) -> None:
         ev[s][2].record()
     stop.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     elapsed_ms = start.elapsed_time(stop)
     sddmm_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / (args.steps * INSTANCES)
     spmm_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / (args.steps * INSTANCES)
@@ -293,6 +294,7 @@ def run_ours(args) -> None:
     e_stop.record()
     barrier()
     e2e_ms = e_start.elapsed_time(e_stop)
+    clocks = sampler.stop() if rank == 0 else None
 
     if dist is not None:
         tt = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
@@ -341,6 +343,12 @@ def run_ours(args) -> None:
                "sample": "1 of %d instances, median of 8 runs after 2 warm-ups; torch.sparse.sampled_addmm + torch.sparse.mm fp32, int32 CSR" % INSTANCES,
                "ms_per_instance": med * 1e3}
 
+    fused_layer = None
+    if world == 1 and not args.no_extras:
+        del dinst, host, host_out
+        torch.cuda.empty_cache()
+        fused_layer = fused_layer_section(dev)
+
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
@@ -349,10 +357,115 @@ def run_ours(args) -> None:
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps},
         "gpu_launches": args.steps * INSTANCES * 2, "clocks": clocks, "kernels": kernels,
+        "fused_layer": fused_layer,
     }
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------------
+# Extra section: benchmark configuration 4, the fused sparse || dense layer (1 GPU)
+# ----------------------------------------------------------------------------------------
+
+def fused_layer_section(dev, iters: int = 20, warmup: int = 5) -> dict:
+    """LLaMA-7B-shaped layer, fp16, 64 tokens: W_up 11008x4096 CSR @50 % and W_qkv 12288x4096
+    dense on the same X 4096x64.  Times (CUDA events, two weight copies rotating so that
+    every launch streams its weights from HBM, 2 x 195 MB > L2): the dense branch, the
+    sparse branch, the serial pair, the two-stream graph interleaving (the reference's
+    method) and the fused launch."""
+    from intrasm_engine_b200 import _lib, synthetic as syn
+    from intrasm_engine_b200.pytorch.cpp_extensions.cuda_graph_constructor import TorchCUDAGraphConstructor
+    MS, MD, K, N = 11008, 12288, 4096, 64
+    a, w, x = syn.fused_layer_case(0, MS, K, N, MD)
+    nnz = a.nnz
+
+    def up(z):
+        return torch.as_tensor(np.ascontiguousarray(z)).to(dev)
+
+    copies = []
+    for _ in range(2):
+        copies.append(dict(ro=up(a.row_offsets), ci=up(a.column_indices), va=up(a.values), w=up(w), x=up(x),
+                           xt=up(np.ascontiguousarray(x.T)),
+                           os=torch.empty((MS, N), dtype=torch.float16, device=dev),
+                           od=torch.empty((N, MD), dtype=torch.float16, device=dev)))
+    st = torch.cuda.current_stream().cuda_stream
+
+    def dense(c, s=None):
+        _lib.call("iex_linear_f16", N, K, MD, c["xt"].data_ptr(), c["w"].data_ptr(), c["od"].data_ptr(), s or st)
+
+    def sparse(c, s=None):
+        _lib.call("iex_spmm_f16_tc", MS, K, N, nnz, c["ro"].data_ptr(), c["ci"].data_ptr(), 16,
+                  c["va"].data_ptr(), c["x"].data_ptr(), c["os"].data_ptr(), s or st)
+
+    def serial(c):
+        dense(c)
+        sparse(c)
+
+    def fused(c):
+        _lib.call("iex_fused_spmm_linear_f16", MS, MD, K, N, nnz, c["ro"].data_ptr(), c["ci"].data_ptr(), 16,
+                  c["va"].data_ptr(), c["w"].data_ptr(), c["x"].data_ptr(), c["os"].data_ptr(),
+                  c["od"].data_ptr(), 1, st)
+
+    # the reference's interleaving: one graph, the two library calls on two captured streams
+    graphs = []
+    for c in copies:
+        ctor = TorchCUDAGraphConstructor()
+        s1 = ctor.register_new_stream()
+        with ctor.get_primary_stream():
+            with ctor:
+                sparse(c, torch.cuda.current_stream().cuda_stream)
+        with s1:
+            with ctor:
+                dense(c, torch.cuda.current_stream().cuda_stream)
+        ctor.join([s1], ctor.get_primary_stream())
+        ctor.instantiate_graph_exec()
+        graphs.append(ctor)
+    gstream = graphs[0].get_primary_stream()
+
+    def timeit(fn, on_graph_stream=False):
+        ctx = gstream if on_graph_stream else torch.cuda.stream(torch.cuda.current_stream())
+        with ctx:
+            for i in range(warmup):
+                fn(i % 2)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(iters):
+                fn(i % 2)
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    us = {
+        "dense_us": timeit(lambda i: dense(copies[i])),
+        "sparse_us": timeit(lambda i: sparse(copies[i])),
+        "serial_us": timeit(lambda i: serial(copies[i])),
+        "interleaved_graph_us": timeit(lambda i: graphs[i].execute_graph(), on_graph_stream=True),
+        "fused_us": timeit(lambda i: fused(copies[i])),
+    }
+    for g in graphs:
+        g.destroy_graph_exec()
+    peak, kind = measured_peak_gbs()
+    bs = syn.spmm_bytes(MS, K, N, nnz, 2, 2)
+    bd = syn.gemm_bytes(MD, N, K)
+    bf = bs + bd - K * N * 2
+    fl = syn.spmm_flops(nnz, N) + syn.gemm_flops(MD, N, K)
+    out = dict(us)
+    out.update({
+        "workload": "cfg4: W_up 11008x4096 CSR@50% (int16 idx) || W_qkv 12288x4096 dense, X 4096x64, fp16",
+        "nnz": nnz, "bytes_sparse": bs, "bytes_dense": bd, "bytes_fused": bf, "peak_gbs": peak, "peak_kind": kind,
+        "fused_vs_serial": us["fused_us"] / us["serial_us"],
+        "fused_vs_interleaved": us["fused_us"] / us["interleaved_graph_us"],
+        "roofline_us": {"sparse": bs / peak * 1e-3, "dense": bd / peak * 1e-3, "shared_hbm_floor": bf / peak * 1e-3},
+        "fused_vs_slower_branch_roofline": us["fused_us"] / (max(bs, bd) / peak * 1e-3),
+        "fused_vs_shared_hbm_floor": us["fused_us"] / (bf / peak * 1e-3),
+        "frac_hbm": {"dense": bd / us["dense_us"] / 1e3 / peak, "sparse": bs / us["sparse_us"] / 1e3 / peak,
+                     "fused": bf / us["fused_us"] / 1e3 / peak},
+        "fused_gflops": fl / us["fused_us"] / 1e3,
+        "status": _lib.lib.iex_last_device_status(1),
+    })
+    return out
 
 
 def main():
@@ -361,6 +474,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the fused-layer section (used for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
