@@ -199,6 +199,7 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
+        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner out of stdout (one JSON line)
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
@@ -333,7 +334,7 @@ def run_ours(args) -> None:
                 "us_per_launch": kernels[dom]["ms"] * 1e3}
 
     cpu = None
-    if world == 1 or rank == 0:
+    if world == 1:
         import warnings
         warnings.filterwarnings("ignore")
         cores = os.cpu_count() or 1

@@ -6,9 +6,13 @@
 //     The grid's y dimension splits long rows: sub-warp y takes tiles y, y+gridDim.y, ...
 //     The grid is sized from nnz/m, not from the dense column count, so no CTA starts
 //     only to find it has nothing to do.
-//   * Lane i reads 4 consecutive k-values (one 128-bit load) of the lhs row and of each
+//   * Lane i reads NV 128-bit vectors (4*NV consecutive k-values) of the lhs row and of each
 //     gathered rhs row, so a rhs row is read as one coalesced segment.  Each lane keeps W
-//     partial dot products (packed f32x2 FMAs), one per nonzero of the tile.
+//     partial dot products (packed f32x2 FMAs), one per nonzero of the tile; all W gathers
+//     of a tile are in flight together, and the next tile's column indices are fetched
+//     while the current tile is computed.  Narrow sub-warps (8 lanes for k <= 64) put four
+//     independent tiles in flight per warp: the kernel is bound by gather latency, so
+//     memory-level parallelism is what counts.
 //   * A butterfly exchange (W-1 shuffles instead of W*log2 W) leaves lane i with the full
 //     dot product of nonzero i, and the tile's W results are stored as one coalesced row.
 //   * Batch items are summed inside the kernel, in batch order: deterministic.
@@ -17,13 +21,15 @@
 namespace iex {
 namespace {
 
-template <int W, bool VEC>
+// NV = 128-bit vectors per lane per pass (0: scalar loads, any k / alignment).
+template <int W, int NV>
 __global__ void __launch_bounds__(128)
 sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
                      const int* __restrict__ row_offsets, const int* __restrict__ cols,
                      const float* __restrict__ lhs, const float* __restrict__ rhs,
                      float* __restrict__ out, int batch, int accumulate) {
-  constexpr int KV = VEC ? 4 : 1;  // k-values per lane per pass
+  constexpr int KV = NV > 0 ? 4 * NV : 1;  // k-values per lane per pass
+  constexpr int NVV = NV > 0 ? NV : 1;
   const int lane = threadIdx.x & 31;
   const int sub = lane / W;
   const int sl = lane % W;
@@ -36,9 +42,15 @@ sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
   const int beg = __ldg(row_offsets + r);
   const int end = __ldg(row_offsets + r + 1);
 
-  for (int p0 = beg + blockIdx.y * W; p0 < end; p0 += gridDim.y * W) {
+  int p0 = beg + blockIdx.y * W;
+  int next_col = (p0 + sl < end) ? __ldg(cols + p0 + sl) : 0;
+  for (; p0 < end; p0 += gridDim.y * W) {
     const int count = min(W, end - p0);
-    const int my_col = (sl < count) ? __ldg(cols + p0 + sl) : 0;
+    const int my_col = next_col;
+    {  // the next tile's indices travel while this tile is computed
+      const int pn = p0 + gridDim.y * W + sl;
+      next_col = (pn < end) ? __ldg(cols + pn) : 0;
+    }
 
     float2 acc[W];
 #pragma unroll
@@ -49,28 +61,30 @@ sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
       const float* b_base = rhs + static_cast<size_t>(z) * n * k;
       for (int kc = 0; kc < k; kc += W * KV) {
         const int kk = kc + sl * KV;
-        const bool in_k = kk < k;
-        float2 a01 = make_float2(0.f, 0.f), a23 = make_float2(0.f, 0.f);
-        if (in_k) {
-          if constexpr (VEC) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(a_row + kk));
-            a01 = make_float2(a.x, a.y);
-            a23 = make_float2(a.z, a.w);
+        float4 a[NVV];
+#pragma unroll
+        for (int v = 0; v < NVV; ++v) {
+          a[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if constexpr (NV > 0) {
+            if (kk + 4 * v < k) a[v] = __ldg(reinterpret_cast<const float4*>(a_row + kk) + v);
           } else {
-            a01.x = __ldg(a_row + kk);
+            if (kk < k) a[v].x = __ldg(a_row + kk);
           }
         }
 #pragma unroll
         for (int j = 0; j < W; ++j) {
           const int cj = __shfl_sync(submask, my_col, j, W);
-          if (j < count && in_k) {
-            const float* b_row = b_base + static_cast<size_t>(cj) * k + kk;
-            if constexpr (VEC) {
-              const float4 b = __ldg(reinterpret_cast<const float4*>(b_row));
-              acc[j] = ffma2(a01, make_float2(b.x, b.y), acc[j]);
-              acc[j] = ffma2(a23, make_float2(b.z, b.w), acc[j]);
+          const float* b_row = b_base + static_cast<size_t>(cj) * k + kk;
+#pragma unroll
+          for (int v = 0; v < NVV; ++v) {
+            if constexpr (NV > 0) {
+              if (j < count && kk + 4 * v < k) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(b_row) + v);
+                acc[j] = ffma2(make_float2(a[v].x, a[v].y), make_float2(b.x, b.y), acc[j]);
+                acc[j] = ffma2(make_float2(a[v].z, a[v].w), make_float2(b.z, b.w), acc[j]);
+              }
             } else {
-              acc[j].x = fmaf(a01.x, __ldg(b_row), acc[j].x);
+              if (j < count && kk < k) acc[j].x = fmaf(a[v].x, __ldg(b_row), acc[j].x);
             }
           }
         }
@@ -99,7 +113,7 @@ sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
   }
 }
 
-template <int W, bool VEC>
+template <int W, int NV>
 int launch(int m, int k, int n, int nnz, const int* ri, const int* ro, const int* cols,
            const float* lhs, const float* rhs, float* out, int batch, int accumulate,
            cudaStream_t stream) {
@@ -109,8 +123,8 @@ int launch(int m, int k, int n, int nnz, const int* ri, const int* ro, const int
   int split = static_cast<int>((avg + 2 * W - 1) / (2 * W));
   split = split < 1 ? 1 : (split > 64 ? 64 : split);
   dim3 grid((m + kRowsPerBlock - 1) / kRowsPerBlock, split, 1);
-  sddmm_rowtile_kernel<W, VEC><<<grid, 128, 0, stream>>>(m, k, n, ri, ro, cols, lhs, rhs,
-                                                         out, batch, accumulate);
+  sddmm_rowtile_kernel<W, NV><<<grid, 128, 0, stream>>>(m, k, n, ri, ro, cols, lhs, rhs, out,
+                                                        batch, accumulate);
   return launch_status();
 }
 
@@ -128,15 +142,16 @@ extern "C" int iex_sddmm_f32(int m, int k, int n, int nnz, const int32_t* row_in
   if (batch > 0 && k > 0 && (!lhs || !rhs)) return IEX_ERR_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool vec = (k % 4 == 0) && aligned16(lhs) && aligned16(rhs);
-#define IEX_GO(W, VEC) \
-  return launch<W, VEC>(m, k, n, nnz, row_indices, row_offsets, column_indices, lhs, rhs, out, batch, accumulate, s)
+#define IEX_GO(W, NV) \
+  return launch<W, NV>(m, k, n, nnz, row_indices, row_offsets, column_indices, lhs, rhs, out, batch, accumulate, s)
   if (vec) {
-    if (k <= 32) { IEX_GO(8, true); }
-    if (k <= 64) { IEX_GO(16, true); }
-    IEX_GO(32, true);
+    if (k <= 32) { IEX_GO(8, 1); }
+    if (k <= 64) { IEX_GO(8, 2); }
+    if (k <= 128) { IEX_GO(16, 2); }
+    IEX_GO(32, 2);
   }
-  if (k <= 8) { IEX_GO(8, false); }
-  if (k <= 16) { IEX_GO(16, false); }
-  IEX_GO(32, false);
+  if (k <= 8) { IEX_GO(8, 0); }
+  if (k <= 16) { IEX_GO(16, 0); }
+  IEX_GO(32, 0);
 #undef IEX_GO
 }

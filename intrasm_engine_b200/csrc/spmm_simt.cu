@@ -60,6 +60,38 @@ __device__ __forceinline__ void store_out(VT* __restrict__ p, const float (&src)
   }
 }
 
+// Raw (unconverted) vector of VD dense elements, so that many gathers can be in flight
+// without holding their fp32 expansion in registers.
+template <typename VT, int VD> struct RawVec;
+template <typename VT> struct RawVec<VT, 1> { VT x; };
+template <> struct RawVec<float, 4> { float4 x; };
+template <> struct RawVec<__half, 8> { uint4 x; };
+
+template <typename VT, int VD>
+__device__ __forceinline__ RawVec<VT, VD> load_raw(const VT* __restrict__ p) {
+  RawVec<VT, VD> r;
+  if constexpr (VD == 1) r.x = __ldg(p);
+  else if constexpr (sizeof(VT) == 4) r.x = __ldg(reinterpret_cast<const float4*>(p));
+  else r.x = __ldg(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+template <typename VT, int VD>
+__device__ __forceinline__ void expand_raw(const RawVec<VT, VD>& r, float (&dst)[VD]) {
+  if constexpr (VD == 1) {
+    dst[0] = to_float(r.x);
+  } else if constexpr (sizeof(VT) == 4) {
+    dst[0] = r.x.x; dst[1] = r.x.y; dst[2] = r.x.z; dst[3] = r.x.w;
+  } else {
+    const __half2* h = reinterpret_cast<const __half2*>(&r.x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      dst[2 * i] = f.x;
+      dst[2 * i + 1] = f.y;
+    }
+  }
+}
+
 // Loads CHS consecutive sparse values / indices starting at element p of the arrays.
 template <typename VT, typename IT, int CHS>
 __device__ __forceinline__ void load_sparse_chunk(const VT* __restrict__ values,
@@ -147,39 +179,61 @@ spmm_rowgroup_kernel(int m, int k, int n, int nnz, const int* __restrict__ row_i
     for (int i = 0; i < (VD + 1) / 2; ++i) acc2[v][i] = make_float2(0.f, 0.f);
   }
 
+  // Memory-level parallelism: the next chunk of the row is loaded while the current one is
+  // consumed, and the gathered dense rows of kJU source lanes (kJU * CHS nonzeros) are all
+  // requested before the first FMA.  Loads are unconditional (padding lanes hold column 0,
+  // a valid row); only the FMAs are predicated, and they run in storage order.
+  constexpr int kWant = 16 / (CHS * NVEC) > 0 ? 16 / (CHS * NVEC) : 1;  // ~16 gathers in flight
+  constexpr int kJU = kWant < LPR ? kWant : LPR;
   int base = VS ? (beg & ~(CHS - 1)) : beg;
+  float v[CHS], vn[CHS];
+  int c[CHS], cn[CHS];
+  load_sparse_chunk<VT, IT, CHS>(values, cols, base + sl * CHS, end, nnz, v, c);
   for (; base < end; base += LPR * CHS) {
-    float v[CHS];
-    int c[CHS];
-    load_sparse_chunk<VT, IT, CHS>(values, cols, base + sl * CHS, end, nnz, v, c);
+    load_sparse_chunk<VT, IT, CHS>(values, cols, base + LPR * CHS + sl * CHS, end, nnz, vn, cn);
     const int remaining = end - base;
     const int src_lanes = min(LPR, (remaining + CHS - 1) / CHS);
-    for (int j = 0; j < src_lanes; ++j) {
+    for (int j0 = 0; j0 < src_lanes; j0 += kJU) {
+      float vv[kJU][CHS];
+      RawVec<VT, VD> b[kJU][CHS][NVEC];
 #pragma unroll
-      for (int e = 0; e < CHS; ++e) {
-        const float vv = __shfl_sync(submask, v[e], j, LPR);
-        const int cc = __shfl_sync(submask, c[e], j, LPR);
-        const int p = base + j * CHS + e;
-        if (p >= beg && p < end) {  // uniform over the row group
+      for (int jj = 0; jj < kJU; ++jj)
+#pragma unroll
+        for (int e = 0; e < CHS; ++e) {
+          const int src = (j0 + jj) & (LPR - 1);
+          vv[jj][e] = __shfl_sync(submask, v[e], src, LPR);
+          const int cc = __shfl_sync(submask, c[e], src, LPR);
           const VT* brow = dense + static_cast<size_t>(cc) * n + col0;
 #pragma unroll
           for (int q = 0; q < NVEC; ++q) {
-            if (col0 + q * LPR * VD < n) {
-              float b[VD];
-              load_dense<VT, VD>(brow + q * LPR * VD, b);
+            // columns past n are never stored; re-read the tile's first vector instead
+            b[jj][e][q] = load_raw<VT, VD>(brow + ((col0 + q * LPR * VD < n) ? q * LPR * VD : 0));
+          }
+        }
+#pragma unroll
+      for (int jj = 0; jj < kJU; ++jj)
+#pragma unroll
+        for (int e = 0; e < CHS; ++e) {
+          const int p = base + (j0 + jj) * CHS + e;
+          if (j0 + jj < LPR && p >= beg && p < end) {  // uniform over the row group
+#pragma unroll
+            for (int q = 0; q < NVEC; ++q) {
+              float bf[VD];
+              expand_raw<VT, VD>(b[jj][e][q], bf);
               if constexpr (VD == 1) {
-                acc1[q] = fmaf(vv, b[0], acc1[q]);
+                acc1[q] = fmaf(vv[jj][e], bf[0], acc1[q]);
               } else {
 #pragma unroll
                 for (int i = 0; i < VD / 2; ++i)
-                  acc2[q][i] = ffma2(make_float2(vv, vv), make_float2(b[2 * i], b[2 * i + 1]),
-                                     acc2[q][i]);
+                  acc2[q][i] = ffma2(make_float2(vv[jj][e], vv[jj][e]),
+                                     make_float2(bf[2 * i], bf[2 * i + 1]), acc2[q][i]);
               }
             }
           }
         }
-      }
     }
+#pragma unroll
+    for (int e = 0; e < CHS; ++e) { v[e] = vn[e]; c[e] = cn[e]; }
   }
 
   const bool fuse_bias = bias != nullptr;

@@ -152,6 +152,23 @@ def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n):
     assert G.close(got, tref, 1e-2, 1e-2)
 
 
+@pytest.mark.parametrize("m,k,n,density", [(4096, 4096, 64, 0.05), (300, 2048, 128, 0.1), (777, 6000, 24, 0.02)])
+def test_spmm_f32_large_operand(oracle, m, k, n, density):
+    """Dense operands far larger than L1 (the gather-latency-bound regime): bit-exact against
+    the oracle, with bias+ReLU and with accumulation."""
+    a, b = syn.spmm_fp32_case(m + k, m, k, n, density)
+    da = G.DevCSR(a)
+    args = (a.row_indices, a.values, a.row_offsets, a.column_indices, b, m)
+    got = G.spmm_f32(da, G.dev(b)[None])[0].cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.spmm(*args)[0])
+    bias = np.linspace(-1, 1, m).astype(np.float32)
+    got = G.spmm_f32(da, G.dev(b)[None], bias=G.dev(bias))[0].cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.spmm(*args, bias=bias)[0])
+    start = np.full((1, m, n), 0.5, np.float32)
+    got = G.spmm_f32(da, G.dev(b)[None], out=G.dev(start), accumulate=True).cpu().numpy()
+    np.testing.assert_array_equal(got, oracle.spmm(*args, out=start))
+
+
 def test_spmm_linearity_and_determinism():
     """Size-independent properties at a size the oracle is not run on."""
     a, b = syn.spmm_fp32_case(3, 4096, 4096, 128, 0.02)
