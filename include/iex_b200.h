@@ -137,6 +137,32 @@ IEX_API int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, i
                                       const void* x, void* out_sparse, void* out_dense,
                                       int dense_out_tokens_major, void* stream);
 
+/* Split-K variants of the three tensor-core entry points.  Every 128-row tile's K range is
+ * cut into `parts` runs handled by different CTAs, so that few-tile problems (a tall-skinny
+ * weight, or 86 decoder-bound sparse tiles on 148 SMs) use the whole GPU.  The fp32 partial
+ * tiles go through `workspace` (device memory, 256-byte aligned, at least
+ * iex_tc_workspace_bytes(...) bytes, contents irrelevant); a second small kernel on the
+ * same stream adds the parts in part order, so results do not depend on timing.  Two
+ * launches that use one workspace must not overlap.  parts = 1 needs no workspace and is
+ * identical to the plain entry point.  With parts > 1 the dense linear needs tokens to be a
+ * multiple of 32.  These have no counterpart in the reference. */
+IEX_API size_t iex_tc_workspace_bytes(int m_sparse, int sparse_parts, int m_dense, int dense_parts,
+                                      int n);
+IEX_API int iex_linear_f16_splitk(int tokens, int in_features, int out_features, const void* input,
+                                  const void* weight, void* out, int parts, void* workspace,
+                                  size_t workspace_bytes, void* stream);
+IEX_API int iex_spmm_f16_tc_splitk(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                                   const void* column_indices, int index_bits, const void* values,
+                                   const void* dense, void* out, int parts, void* workspace,
+                                   size_t workspace_bytes, void* stream);
+IEX_API int iex_fused_spmm_linear_f16_splitk(int m_sparse, int m_dense, int k, int n, int nnz,
+                                             const int32_t* row_offsets, const void* column_indices,
+                                             int index_bits, const void* values, const void* weight,
+                                             const void* x, void* out_sparse, void* out_dense,
+                                             int dense_out_tokens_major, int sparse_parts,
+                                             int dense_parts, void* workspace, size_t workspace_bytes,
+                                             void* stream);
+
 /* Last device-side failure recorded by any kernel of this library (0 = none).
  * Synchronises the device.  clear != 0 resets the word. */
 IEX_API int iex_last_device_status(int clear);

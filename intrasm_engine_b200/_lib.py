@@ -41,6 +41,14 @@ SIGNATURES = {
     # dense_out_tokens_major stream
     "iex_fused_spmm_linear_f16": (c_int, [c_int, c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int,
                                           c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    "iex_tc_workspace_bytes": (c_size, [c_int, c_int, c_int, c_int, c_int]),
+    # ... parts workspace workspace_bytes stream
+    "iex_linear_f16_splitk": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_size, c_ptr]),
+    "iex_spmm_f16_tc_splitk": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
+                                       c_ptr, c_int, c_ptr, c_size, c_ptr]),
+    "iex_fused_spmm_linear_f16_splitk": (c_int, [c_int, c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int,
+                                                 c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int,
+                                                 c_ptr, c_size, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)
     "iex_graph_create": (c_ptr, []),

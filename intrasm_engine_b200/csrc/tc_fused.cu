@@ -61,6 +61,12 @@ struct Params {
   int k, n;
   int num_stages, tmem_cols;
   int* status;
+  // split-K: every tile's K range is cut into `parts` equal runs of k-blocks, one unit
+  // each.  With parts > 1 a unit writes its fp32 partial tile to `partials`
+  // ([tile][part][128][n], sparse tiles first) and a second, tiny kernel adds the parts in
+  // part order and writes the fp16 output.
+  int s_parts, d_parts;
+  float* partials;
 };
 
 __device__ int g_status = 0;  // last device-side failure (IEX_ERR_TIMEOUT) of this library
@@ -156,18 +162,30 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Position u of the work list -> (is_sparse, tile).  The list is
+// Position u of the work list -> (is_sparse, tile, part).  With S = s_tiles * s_parts sparse
+// units and D = d_tiles * d_parts dense units the list is
 //   dense[0, e)  ++  sparse[0, S)  ++  dense[e, D)      with e = clamp(D + S - grid, 0, D),
 // and CTA c takes positions c, c + grid, ...  Sparse units are the long ones (their cost
-// is decoder instructions), so with at most two waves the CTAs that get a second unit
-// are the ones that started with a (short) dense unit.
-__device__ __forceinline__ void unit_of(int u, int d_tiles, int s_tiles, int grid, bool& sparse,
-                                        int& tile) {
-  int e = d_tiles + s_tiles - grid;
-  e = e < 0 ? 0 : (e > d_tiles ? d_tiles : e);
-  if (u < e) { sparse = false; tile = u; }
-  else if (u < e + s_tiles) { sparse = true; tile = u - e; }
-  else { sparse = false; tile = u - s_tiles; }
+// is decoder work), so with at most two waves the CTAs that get a second unit are the ones
+// that started with a (short) dense unit.  Parts of one tile are neighbours in the list,
+// so they run at the same time and reach the reduction together.
+struct Unit {
+  bool sparse;
+  int tile, part, parts;
+};
+__device__ __forceinline__ Unit unit_of(int u, const Params& prm, int grid) {
+  const int S = prm.s_tiles * prm.s_parts, D = prm.d_tiles * prm.d_parts;
+  int e = D + S - grid;
+  e = e < 0 ? 0 : (e > D ? D : e);
+  Unit un;
+  int idx;
+  if (u < e) { un.sparse = false; idx = u; }
+  else if (u < e + S) { un.sparse = true; idx = u - e; }
+  else { un.sparse = false; idx = u - S; }
+  un.parts = un.sparse ? prm.s_parts : prm.d_parts;
+  un.tile = idx / un.parts;
+  un.part = idx - un.tile * un.parts;
+  return un;
 }
 
 // Eight consecutive nonzeros of one row as loaded: raw fp16 bit patterns and indices.
@@ -276,6 +294,29 @@ __device__ __forceinline__ int group8_sum(int v, unsigned) {
   return v;
 }
 
+// First position p in [lo, hi) with cols[p] >= key (hi when there is none), found by the 8
+// lanes of a row group together: each step probes 8 evenly spaced positions and keeps the
+// ninth of the range that holds the answer.  All lanes of the group return the same value.
+template <typename IT>
+__device__ __forceinline__ int group_lower_bound(const IT* __restrict__ cols, int lo, int hi, int key,
+                                                 int sl, unsigned gmask) {
+  const int shift = __ffs(gmask) - 1;
+  while (hi - lo > 8) {
+    const int step = (hi - lo + 8) / 9;            // >= 1; the probes split [lo, hi) into <= 9 runs
+    const int pos = lo + (sl + 1) * step - 1;       // last element of run sl
+    const bool below = pos < hi && to_index(__ldg(cols + pos)) < key;
+    const unsigned b = (__ballot_sync(gmask, below) >> shift) & 0xffu;
+    const int nb = __popc(b);                       // monotone: the first nb probes are below
+    const int new_lo = lo + nb * step;
+    const int new_hi = min(hi, lo + (nb + 1) * step);
+    lo = new_lo > hi ? hi : new_lo;
+    hi = new_hi;
+  }
+  const bool below = lo + sl < hi && to_index(__ldg(cols + lo + sl)) < key;
+  const unsigned b = (__ballot_sync(gmask, below) >> shift) & 0xffu;
+  return lo + __popc(b);
+}
+
 // ND = number of CSR decoder warps (0: dense-only instance).
 template <int ND, typename IT>
 __global__ void __launch_bounds__((kFirstDecodeWarp + ND) * 32, 1)
@@ -304,7 +345,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_units = prm.d_tiles + prm.s_tiles;
+  const int total_units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
   const int k_blocks = (prm.k + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -338,12 +379,13 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-        bool sparse;
-        int tile;
-        unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
+        const Unit un = unit_of(u, prm, gridDim.x);
+        const bool sparse = un.sparse;
+        const int tile = un.tile;
+        const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
         const bool b_mn = sparse || prm.d_b_mn;
         const CUtensorMap* tmb = sparse ? &tma_b_sparse : &tma_b_dense;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
@@ -376,14 +418,13 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       uint32_t it = 0, unit_it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
-        bool sparse;
-        int tile;
-        unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
-        const bool b_mn = sparse || prm.d_b_mn;
+        const Unit un = unit_of(u, prm, gridDim.x);
+        const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
+        const bool b_mn = un.sparse || prm.d_b_mn;
         const uint32_t idesc = b_mn ? idesc_mn : idesc_k;
         if (!mbar_wait(accum_empty, (unit_it & 1u) ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
         tcgen05_fence_after();
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % S;
           const uint32_t ph = (it / S) & 1u;
           if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
@@ -397,7 +438,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const uint64_t bdesc =
                 b_mn ? smem_desc(b_base + ks * (UMMA_K * 128), BK * 128, 1024)
                      : smem_desc(b_base + (ks >> 2) * (n * 128) + (ks & 3) * 32, 16, 1024);
-            umma_f16(tmem_base, adesc, bdesc, idesc, (kb | ks) != 0 ? 1u : 0u);
+            umma_f16(tmem_base, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
           }
           umma_commit(empty_bar(s));
         }
@@ -410,16 +451,22 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     uint32_t unit_it = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
-      bool sparse;
-      int tile;
-      unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
+      const Unit un = unit_of(u, prm, gridDim.x);
+      const bool sparse = un.sparse;
+      const int tile = un.tile;
       if (!mbar_wait(accum_full, unit_it & 1u, abort_flag, prm.status, 256)) { ok = false; break; }
       tcgen05_fence_after();
-      const int row = tile * BM + q * 32 + lane;
+      const int row_local = q * 32 + lane;
+      const int row = tile * BM + row_local;
       const int rows = sparse ? prm.s_m : prm.d_m;
       __half* out = sparse ? prm.s_out : prm.d_out;
       const long long sm = sparse ? static_cast<long long>(n) : prm.d_stride_m;
       const long long sn = sparse ? 1ll : prm.d_stride_n;
+      // partial tiles of this output tile: [part][128 rows][n] fp32
+      float* part_base = prm.partials == nullptr ? nullptr
+          : prm.partials + (static_cast<size_t>(sparse ? tile * prm.s_parts
+                                                        : prm.s_tiles * prm.s_parts + tile * prm.d_parts)) *
+                               (static_cast<size_t>(BM) * n);
       for (int c0 = 0; c0 < n; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
@@ -429,7 +476,14 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(accum_empty);
         }
-        if (row < rows) {
+        if (un.parts > 1) {
+          float4* dst = reinterpret_cast<float4*>(
+              part_base + (static_cast<size_t>(un.part) * BM + row_local) * n + c0);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        } else if (row < rows) {
           if (sn == 1) {
             uint4* dst = reinterpret_cast<uint4*>(out + row * sm + c0);
 #pragma unroll
@@ -473,9 +527,10 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     uint32_t it = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-      bool sparse;
-      int tile;
-      unit_of(u, prm.d_tiles, prm.s_tiles, gridDim.x, sparse, tile);
+      const Unit un = unit_of(u, prm, gridDim.x);
+      const bool sparse = un.sparse;
+      const int tile = un.tile;
+      const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
       int cur[kIters], rend[kIters], rstart[kIters], filled[kIters];
       uint32_t vring[kIters], cring[kIters];
       if (sparse) {
@@ -487,9 +542,11 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           rstart[i] = in ? __ldg(prm.s_row_offsets + row) : 0;
           rend[i] = in ? __ldg(prm.s_row_offsets + row + 1) : 0;
           cur[i] = rstart[i];
+          if (kb0 > 0)  // this part starts inside the row: first nonzero with column >= kb0 * BK
+            cur[i] = group_lower_bound<IT>(cols, rstart[i], rend[i], kb0 * BK, sl, gmask);
           vring[i] = ring_base + row_local * (kRing * 2u);
           cring[i] = ring_base + BM * (kRing * 2u) + row_local * (kRing * static_cast<uint32_t>(sizeof(IT)));
-          const int g0 = rstart[i] >> 3;
+          const int g0 = cur[i] >> 3;
           ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + sl, rend[i], nnz);
           ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + 8 + sl, rend[i], nnz);
           filled[i] = g0 + kRingGranules;
@@ -497,7 +554,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");  // so that wait_group 1 covers the fill
       }
-      for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
         if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 32)) { ok = false; break; }
@@ -586,6 +643,63 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   }
 }
 
+// Second pass of split-K: out tile = sum over parts (in part order) of the fp32 partial
+// tiles, converted to fp16.  grid = (split tiles, kReduceSlices): every CTA sweeps one
+// slice of a tile as a flat array of float4 (coalesced), with the loads of four parts in
+// flight per thread.
+constexpr int kReduceSlices = 8;
+constexpr int kReduceThreads = 256;
+
+__global__ void __launch_bounds__(kReduceThreads)
+tc_reduce_kernel(const Params prm) {
+  const int n = prm.n;
+  const int s_split = prm.s_parts > 1 ? prm.s_tiles : 0;
+  const bool sparse = static_cast<int>(blockIdx.x) < s_split;
+  const int tile = sparse ? blockIdx.x : blockIdx.x - s_split;
+  const int parts = sparse ? prm.s_parts : prm.d_parts;
+  const int rows = sparse ? prm.s_m : prm.d_m;
+  __half* out = sparse ? prm.s_out : prm.d_out;
+  const long long sm = sparse ? static_cast<long long>(n) : prm.d_stride_m;
+  const long long sn = sparse ? 1ll : prm.d_stride_n;
+  const size_t part_stride = static_cast<size_t>(BM) * n;
+  const float* base = prm.partials +
+      static_cast<size_t>(sparse ? tile * prm.s_parts : prm.s_tiles * prm.s_parts + tile * prm.d_parts) *
+          part_stride;
+  const int vec_per_row = n >> 2;
+  const int total_vecs = BM * vec_per_row;
+  for (int f = blockIdx.y * kReduceThreads + threadIdx.x; f < total_vecs; f += kReduceSlices * kReduceThreads) {
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    int pp = 0;
+    for (; pp + 4 <= parts; pp += 4) {
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        t[u] = __ldcg(reinterpret_cast<const float4*>(base + (pp + u) * part_stride) + f);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
+    }
+    for (; pp < parts; ++pp) {
+      const float4 t = __ldcg(reinterpret_cast<const float4*>(base + pp * part_stride) + f);
+      sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+    }
+    const int rl = f / vec_per_row, c4 = (f - rl * vec_per_row) * 4;
+    const int orow = tile * BM + rl;
+    if (orow >= rows) continue;
+    if (sn == 1) {
+      uint2 pk;
+      __half2* h = reinterpret_cast<__half2*>(&pk);
+      h[0] = __floats2half2_rn(sum.x, sum.y);
+      h[1] = __floats2half2_rn(sum.z, sum.w);
+      *reinterpret_cast<uint2*>(out + orow * sm + c4) = pk;
+    } else {
+      out[orow * sm + (c4 + 0) * sn] = __float2half_rn(sum.x);
+      out[orow * sm + (c4 + 1) * sn] = __float2half_rn(sum.y);
+      out[orow * sm + (c4 + 2) * sn] = __float2half_rn(sum.z);
+      out[orow * sm + (c4 + 3) * sn] = __float2half_rn(sum.w);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
@@ -655,7 +769,13 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
   const int units = prm.d_tiles + prm.s_tiles;
   const int grid = units < sm_count() * ctas_per_sm ? units : sm_count() * ctas_per_sm;
   kern<<<grid, (kFirstDecodeWarp + ND) * 32, smem, stream>>>(ta, tbd, tbs, prm);
-  return launch_status();
+  int st = launch_status();
+  const int split_tiles = (prm.s_parts > 1 ? prm.s_tiles : 0) + (prm.d_parts > 1 ? prm.d_tiles : 0);
+  if (st == 0 && split_tiles > 0) {
+    tc_reduce_kernel<<<dim3(split_tiles, kReduceSlices), kReduceThreads, 0, stream>>>(prm);
+    st = launch_status();
+  }
+  return st;
 }
 
 int tmem_cols_for(int n) {
@@ -680,37 +800,6 @@ extern "C" int iex_last_device_status(int clear) {
   return v;
 }
 
-extern "C" int iex_linear_f16(int tokens, int in_features, int out_features, const void* input,
-                              const void* weight, void* out, void* stream) {
-  if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
-  if (tokens == 0 || out_features == 0) return IEX_OK;
-  if (!input || !weight || !out) return IEX_ERR_BAD_ARG;
-  if (tokens % 16 != 0 || tokens > 256 || in_features % 8 != 0 || in_features == 0)
-    return IEX_ERR_UNSUPPORTED;
-  if (!aligned16(input) || !aligned16(weight)) return IEX_ERR_UNSUPPORTED;
-  CUtensorMap ta, tb;
-  int st = make_map(&ta, weight, out_features, in_features, BM);
-  if (st) return st;
-  st = make_map(&tb, input, tokens, in_features, tokens);
-  if (st) return st;
-  Params p{};
-  p.d_tiles = (out_features + BM - 1) / BM;
-  p.d_m = out_features;
-  p.d_out = static_cast<__half*>(out);
-  p.d_stride_m = 1;
-  p.d_stride_n = out_features;
-  p.d_b_mn = 0;
-  p.k = in_features;
-  p.n = tokens;
-  p.tmem_cols = tmem_cols_for(tokens);
-  p.status = status_word();
-  const int stage_bytes = A_STAGE_BYTES + tokens * 256;
-  int stages = (220 * 1024) / stage_bytes;
-  stages = stages > 6 ? 6 : stages;
-  if (stages < 2) return IEX_ERR_UNSUPPORTED;
-  return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
-}
-
 namespace {
 
 // Stages that fit beside the CSR rings in one CTA's shared memory (one CTA per SM).
@@ -733,41 +822,65 @@ int sparse_args_ok(int m, int k, int n, int nnz, const int32_t* row_offsets, con
   return IEX_OK;
 }
 
-}  // namespace
-
-extern "C" int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_offsets,
-                               const void* column_indices, int index_bits, const void* values,
-                               const void* dense, void* out, void* stream) {
-  if (m == 0) return IEX_OK;
-  int st = sparse_args_ok(m, k, n, nnz, row_offsets, column_indices, values, dense, out, index_bits);
-  if (st) return st;
-  CUtensorMap tb;
-  st = make_map(&tb, dense, k, n, BK);
-  if (st) return st;
-  Params p{};
-  p.s_tiles = (m + BM - 1) / BM;
-  p.s_m = m;
-  p.s_nnz = nnz;
-  p.s_out = static_cast<__half*>(out);
-  p.s_row_offsets = row_offsets;
-  p.s_cols = column_indices;
-  p.s_values = static_cast<const __half*>(values);
-  p.k = k;
-  p.n = n;
-  p.tmem_cols = tmem_cols_for(n);
-  p.status = status_word();
-  const int stages = sparse_stages(n, index_bits);
-  if (stages < 2) return IEX_ERR_UNSUPPORTED;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (index_bits == 16) return launch_units<kDecodeWarps, uint16_t>(tb, tb, tb, p, stages, 1, s);
-  return launch_units<kDecodeWarps, int>(tb, tb, tb, p, stages, 1, s);
+size_t workspace_bytes(int s_tiles, int s_parts, int d_tiles, int d_parts, int n) {
+  if (s_parts <= 1 && d_parts <= 1) return 0;
+  return (static_cast<size_t>(s_tiles) * s_parts + static_cast<size_t>(d_tiles) * d_parts) * BM * n * 4;
 }
 
-extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, int nnz,
-                                         const int32_t* row_offsets, const void* column_indices,
-                                         int index_bits, const void* values, const void* weight,
-                                         const void* x, void* out_sparse, void* out_dense,
-                                         int dense_out_tokens_major, void* stream) {
+// Clamps the part counts to the number of k-blocks and points the kernel at the workspace.
+int bind_workspace(Params& p, int s_parts, int d_parts, void* workspace, size_t bytes) {
+  const int k_blocks = (p.k + BK - 1) / BK;
+  p.s_parts = s_parts < 1 ? 1 : (s_parts > k_blocks ? k_blocks : s_parts);
+  p.d_parts = d_parts < 1 ? 1 : (d_parts > k_blocks ? k_blocks : d_parts);
+  if (p.s_tiles == 0) p.s_parts = 1;
+  if (p.d_tiles == 0) p.d_parts = 1;
+  const size_t need = workspace_bytes(p.s_tiles, p.s_parts, p.d_tiles, p.d_parts, p.n);
+  p.partials = nullptr;
+  if (need == 0) return IEX_OK;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return IEX_ERR_BAD_ARG;
+  if (bytes < need) return IEX_ERR_TOO_LARGE;
+  p.partials = static_cast<float*>(workspace);
+  return IEX_OK;
+}
+
+int linear_impl(int tokens, int in_features, int out_features, const void* input, const void* weight,
+                void* out, int parts, void* workspace, size_t bytes, void* stream) {
+  if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
+  if (tokens == 0 || out_features == 0) return IEX_OK;
+  if (!input || !weight || !out) return IEX_ERR_BAD_ARG;
+  if (tokens % 16 != 0 || tokens > 256 || in_features % 8 != 0 || in_features == 0)
+    return IEX_ERR_UNSUPPORTED;
+  if (!aligned16(input) || !aligned16(weight)) return IEX_ERR_UNSUPPORTED;
+  if (parts > 1 && tokens % 32 != 0) return IEX_ERR_UNSUPPORTED;  // partial tiles are 32 columns wide
+  CUtensorMap ta, tb;
+  int st = make_map(&ta, weight, out_features, in_features, BM);
+  if (st) return st;
+  st = make_map(&tb, input, tokens, in_features, tokens);
+  if (st) return st;
+  Params p{};
+  p.d_tiles = (out_features + BM - 1) / BM;
+  p.d_m = out_features;
+  p.d_out = static_cast<__half*>(out);
+  p.d_stride_m = 1;
+  p.d_stride_n = out_features;
+  p.d_b_mn = 0;
+  p.k = in_features;
+  p.n = tokens;
+  p.tmem_cols = tmem_cols_for(tokens);
+  p.status = status_word();
+  st = bind_workspace(p, 1, parts, workspace, bytes);
+  if (st) return st;
+  const int stage_bytes = A_STAGE_BYTES + tokens * 256;
+  int stages = (220 * 1024) / stage_bytes;
+  stages = stages > 6 ? 6 : stages;
+  if (stages < 2) return IEX_ERR_UNSUPPORTED;
+  return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
+}
+
+int fused_impl(int m_sparse, int m_dense, int k, int n, int nnz, const int32_t* row_offsets,
+               const void* column_indices, int index_bits, const void* values, const void* weight,
+               const void* x, void* out_sparse, void* out_dense, int dense_out_tokens_major,
+               int sparse_parts, int dense_parts, void* workspace, size_t bytes, void* stream) {
   if (m_dense < 0 || m_sparse < 0) return IEX_ERR_BAD_ARG;
   int st;
   if (m_sparse > 0) {
@@ -808,9 +921,70 @@ extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n
   p.n = n;
   p.tmem_cols = tmem_cols_for(n);
   p.status = status_word();
+  st = bind_workspace(p, sparse_parts, dense_parts, workspace, bytes);
+  if (st) return st;
   const int stages = sparse_stages(n, index_bits);
   if (stages < 2) return IEX_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (index_bits == 16) return launch_units<kDecodeWarps, uint16_t>(ta, tb, tb, p, stages, 1, s);
   return launch_units<kDecodeWarps, int>(ta, tb, tb, p, stages, 1, s);
+}
+
+}  // namespace
+
+extern "C" size_t iex_tc_workspace_bytes(int m_sparse, int sparse_parts, int m_dense, int dense_parts,
+                                         int n) {
+  if (m_sparse < 0 || m_dense < 0 || n < 0) return 0;
+  return workspace_bytes((m_sparse + BM - 1) / BM, sparse_parts < 1 ? 1 : sparse_parts,
+                         (m_dense + BM - 1) / BM, dense_parts < 1 ? 1 : dense_parts, n);
+}
+
+extern "C" int iex_linear_f16(int tokens, int in_features, int out_features, const void* input,
+                              const void* weight, void* out, void* stream) {
+  return linear_impl(tokens, in_features, out_features, input, weight, out, 1, nullptr, 0, stream);
+}
+
+extern "C" int iex_linear_f16_splitk(int tokens, int in_features, int out_features, const void* input,
+                                     const void* weight, void* out, int parts, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  return linear_impl(tokens, in_features, out_features, input, weight, out, parts, workspace,
+                     workspace_bytes, stream);
+}
+
+extern "C" int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                               const void* column_indices, int index_bits, const void* values,
+                               const void* dense, void* out, void* stream) {
+  if (m == 0) return IEX_OK;
+  return fused_impl(m, 0, k, n, nnz, row_offsets, column_indices, index_bits, values, nullptr, dense, out,
+                    nullptr, 1, 1, 1, nullptr, 0, stream);
+}
+
+extern "C" int iex_spmm_f16_tc_splitk(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                                      const void* column_indices, int index_bits, const void* values,
+                                      const void* dense, void* out, int parts, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  if (m == 0) return IEX_OK;
+  return fused_impl(m, 0, k, n, nnz, row_offsets, column_indices, index_bits, values, nullptr, dense, out,
+                    nullptr, 1, parts, 1, workspace, workspace_bytes, stream);
+}
+
+extern "C" int iex_fused_spmm_linear_f16(int m_sparse, int m_dense, int k, int n, int nnz,
+                                         const int32_t* row_offsets, const void* column_indices,
+                                         int index_bits, const void* values, const void* weight,
+                                         const void* x, void* out_sparse, void* out_dense,
+                                         int dense_out_tokens_major, void* stream) {
+  return fused_impl(m_sparse, m_dense, k, n, nnz, row_offsets, column_indices, index_bits, values, weight, x,
+                    out_sparse, out_dense, dense_out_tokens_major, 1, 1, nullptr, 0, stream);
+}
+
+extern "C" int iex_fused_spmm_linear_f16_splitk(int m_sparse, int m_dense, int k, int n, int nnz,
+                                                const int32_t* row_offsets, const void* column_indices,
+                                                int index_bits, const void* values, const void* weight,
+                                                const void* x, void* out_sparse, void* out_dense,
+                                                int dense_out_tokens_major, int sparse_parts,
+                                                int dense_parts, void* workspace, size_t workspace_bytes,
+                                                void* stream) {
+  return fused_impl(m_sparse, m_dense, k, n, nnz, row_offsets, column_indices, index_bits, values, weight, x,
+                    out_sparse, out_dense, dense_out_tokens_major, sparse_parts, dense_parts, workspace,
+                    workspace_bytes, stream);
 }

@@ -182,3 +182,58 @@ def test_torch_ops_tc(oracle):
     assert G.close(out_s.cpu().numpy(), ref_s, RTOL, RTOL)
     with pytest.raises(RuntimeError):
         ops.linear_fp16(xs.t().contiguous().float(), ws)
+
+
+# ----------------------------------------------------------------------------------------
+# split-K entry points (fp32 partial tiles in a caller-provided workspace + reduce kernel)
+# ----------------------------------------------------------------------------------------
+
+def _workspace(nbytes):
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=G.DEV)
+
+
+@pytest.mark.parametrize("tokens,cin,cout,parts", [(64, 4096, 2048, 4), (32, 1024, 1000, 3), (256, 2048, 512, 8),
+                                                   (64, 256, 128, 16), (128, 640, 384, 2)])
+def test_linear_splitk(tokens, cin, cout, parts):
+    rng = np.random.default_rng(tokens + cin + cout)
+    x = G.dev(rng.standard_normal((tokens, cin)).astype(np.float16))
+    w = G.dev((rng.standard_normal((cout, cin)) * 0.05).astype(np.float16))
+    ref = x.float() @ w.float().t()
+    need = _lib.lib.iex_tc_workspace_bytes(0, 1, cout, parts, tokens)
+    ws = _workspace(need)
+    out = torch.zeros((tokens, cout), dtype=torch.float16, device=G.DEV)
+    for _ in range(2):  # the workspace is reusable without clearing
+        _lib.call("iex_linear_f16_splitk", tokens, cin, cout, x.data_ptr(), w.data_ptr(), out.data_ptr(),
+                  parts, ws.data_ptr(), ws.numel(), G.stream_ptr())
+        assert G.close(out.cpu().numpy(), ref.cpu().numpy(), RTOL, RTOL)
+    assert torch.allclose(out.float(), _linear(x, w).float(), rtol=2e-3, atol=2e-3 * float(ref.abs().max()))
+    if need > 256 and parts <= (cin + 127) // 128:  # the kernel never uses more parts than k-blocks
+        with pytest.raises(_lib.IexError) as e:
+            _lib.call("iex_linear_f16_splitk", tokens, cin, cout, x.data_ptr(), w.data_ptr(), out.data_ptr(),
+                      parts, ws.data_ptr(), need - 1, G.stream_ptr())
+        assert e.value.status == -3
+    _status_clean()
+
+
+@pytest.mark.parametrize("parts", [2, 3, 5])
+def test_spmm_tc_and_fused_splitk(oracle, parts):
+    a, w, x = syn.fused_layer_case(11, 640, 1024, 64, 384)
+    da = G.DevCSR(a)
+    xd, wd = G.dev(x), G.dev(w)
+    ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, 640)[0]
+    ref_d = x.astype(np.float32).T @ w.astype(np.float32).T
+    ws = _workspace(_lib.lib.iex_tc_workspace_bytes(640, parts, 384, 2, 64))
+    out_s = torch.zeros((640, 64), dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_spmm_f16_tc_splitk", 640, 1024, 64, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
+              16, da.values.data_ptr(), xd.data_ptr(), out_s.data_ptr(), parts, ws.data_ptr(), ws.numel(),
+              G.stream_ptr())
+    assert G.close(out_s.cpu().numpy(), ref_s, RTOL, RTOL)
+    first = out_s.clone()
+    out_s.zero_()
+    out_d = torch.zeros((64, 384), dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_fused_spmm_linear_f16_splitk", 640, 384, 1024, 64, a.nnz, da.row_offsets.data_ptr(),
+              da.column_indices.data_ptr(), 16, da.values.data_ptr(), wd.data_ptr(), xd.data_ptr(),
+              out_s.data_ptr(), out_d.data_ptr(), 1, parts, 2, ws.data_ptr(), ws.numel(), G.stream_ptr())
+    assert torch.equal(out_s, first)  # parts are added in part order: same bits in either launch
+    assert G.close(out_d.cpu().numpy(), ref_d, RTOL, RTOL)
+    _status_clean()
