@@ -163,6 +163,25 @@ IEX_API int iex_fused_spmm_linear_f16_splitk(int m_sparse, int m_dense, int k, i
                                              int dense_parts, void* workspace, size_t workspace_bytes,
                                              void* stream);
 
+/* iex_linear_f16_splitk for callers that cannot hand over a workspace because they may
+ * not allocate device memory while running (a serving process or plugin host whose memory
+ * budget is fixed at start-up and which bans later cudaMalloc calls, since those
+ * synchronise the device and may fail under fragmentation).  No counterpart in the
+ * reference.  Same arguments and results as iex_linear_f16_splitk minus the workspace: the
+ * partial tiles go to a fixed array inside the library, iex_static_workspace_capacity()
+ * bytes (8 MiB) on every GPU that loads the library, held until the process exits.  The
+ * call allocates and frees nothing, neither directly nor through a library.  It returns
+ * IEX_ERR_TOO_LARGE when ceil(out_features / 128) * parts * 128 * tokens * 4 bytes exceed
+ * that capacity.  The first call on a device looks the array's address up (a runtime
+ * query, once per device, with that device current); make that first call before any
+ * stream capture.  All calls on a device share the one array and each overwrites what the
+ * previous left (nothing in it has to start at zero): two calls that overlap on the GPU
+ * race, so keep them on one stream or order them with events. */
+IEX_API size_t iex_static_workspace_capacity(void);
+IEX_API int iex_linear_f16_splitk_static(int tokens, int in_features, int out_features,
+                                         const void* input, const void* weight, void* out,
+                                         int parts, void* stream);
+
 /* Last device-side failure recorded by any kernel of this library (0 = none).
  * Synchronises the device.  clear != 0 resets the word. */
 IEX_API int iex_last_device_status(int clear);

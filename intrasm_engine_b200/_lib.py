@@ -49,6 +49,9 @@ SIGNATURES = {
     "iex_fused_spmm_linear_f16_splitk": (c_int, [c_int, c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int,
                                                  c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int, c_int,
                                                  c_ptr, c_size, c_ptr]),
+    "iex_static_workspace_capacity": (c_size, []),
+    # tokens in_features out_features input weight out parts stream
+    "iex_linear_f16_splitk_static": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)
     "iex_graph_create": (c_ptr, []),

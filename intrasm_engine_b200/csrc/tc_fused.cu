@@ -31,6 +31,8 @@
 // frees its TMEM and returns.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace iex {
@@ -987,4 +989,70 @@ extern "C" int iex_fused_spmm_linear_f16_splitk(int m_sparse, int m_dense, int k
   return fused_impl(m_sparse, m_dense, k, n, nnz, row_offsets, column_indices, index_bits, values, weight, x,
                     out_sparse, out_dense, dense_out_tokens_major, sparse_parts, dense_parts, workspace,
                     workspace_bytes, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Split-K linear without any allocation by anybody
+//
+// Some hosts of this library may not create device memory once they are running: a serving
+// process or plugin host that sizes its memory pool at start-up and forbids later
+// cudaMalloc calls (they synchronise the whole device and can fail once memory is
+// fragmented), or a caller that has no allocator of its own to take a workspace from.
+// For them the partial tiles of iex_linear_f16_splitk live in the fixed array below, which
+// every GPU that loads this library carries until the process exits.
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticWorkspaceBytes = size_t(8) << 20;  // 8 MiB per device
+constexpr int kMaxDevices = 64;
+
+}  // namespace
+
+// In host code this name is only a handle for cudaGetSymbolAddress, not a device pointer.
+static __device__ __align__(256) unsigned char g_static_workspace[kStaticWorkspaceBytes];
+
+namespace {
+
+std::mutex g_static_mutex;
+void* g_static_address[kMaxDevices] = {};
+
+// Device address of g_static_workspace on the CURRENT device, looked up once per device.
+int static_workspace_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return IEX_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_address[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_workspace);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (p == nullptr) return IEX_ERR_DRIVER;
+    g_static_address[dev] = p;
+  }
+  *out = g_static_address[dev];
+  return IEX_OK;
+}
+
+}  // namespace
+
+extern "C" size_t iex_static_workspace_capacity(void) { return kStaticWorkspaceBytes; }
+
+extern "C" int iex_linear_f16_splitk_static(int tokens, int in_features, int out_features,
+                                            const void* input, const void* weight, void* out, int parts,
+                                            void* stream) {
+  if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
+  // Size check first, with the part count the kernel will really use (never more than k-blocks).
+  const int k_blocks = (in_features + BK - 1) / BK;
+  int used_parts = parts < 1 ? 1 : parts;
+  if (used_parts > k_blocks) used_parts = k_blocks > 0 ? k_blocks : 1;
+  const size_t need = workspace_bytes(0, 1, (out_features + BM - 1) / BM, used_parts, tokens);
+  if (need > kStaticWorkspaceBytes) return IEX_ERR_TOO_LARGE;
+  void* ws = nullptr;
+  if (need > 0) {
+    const int st = static_workspace_address(&ws);
+    if (st != IEX_OK) return st;
+  }
+  return linear_impl(tokens, in_features, out_features, input, weight, out, used_parts, ws,
+                     need > 0 ? kStaticWorkspaceBytes : 0, stream);
 }
