@@ -276,12 +276,35 @@ def run_ours(args) -> None:
     h2d = sum(sum(t.numel() * t.element_size() for t in h) for h in host)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 
+    # Two device staging slots: the host->device copy of instance i+1 runs on a copy stream
+    # while instance i is computed; events order slot reuse.  The operator calls are the
+    # public torch ops on the current stream.
+    copy_stream = torch.cuda.Stream(device=dev)
+    slots = [[torch.empty_like(t, device=dev) for t in host[0]] for _ in range(2)]
+    max_nnz = max(h[5].numel() for h in host)
+    for sl_ in slots:
+        sl_[5] = torch.empty(max_nnz, dtype=torch.int32, device=dev)
+    ready = [torch.cuda.Event() for _ in range(2)]
+    free = [torch.cuda.Event() for _ in range(2)]
+
     def e2e_step():
-        for h, ho in zip(host, host_out):
-            q, k, v, ri, ro, ci = (t.to(dev, non_blocking=True) for t in h)
+        cur = torch.cuda.current_stream()
+        for i, (h, ho) in enumerate(zip(host, host_out)):
+            b = i & 1
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(free[b])
+                views = []
+                for dst, src in zip(slots[b], h):
+                    v = dst[:src.numel()] if dst.dim() == 1 else dst
+                    v.copy_(src, non_blocking=True)
+                    views.append(v)
+                ready[b].record(copy_stream)
+            cur.wait_event(ready[b])
+            q, k, v, ri, ro, ci = views
             scores = ops.sddmm_sputnik_atomic_upd_weight(q[None], k[None], ri, ro, ci)
             out = ops.spmm_sputnik_reuse_weight(v[None], ri, scores, ro, ci, M)
             ho.copy_(out[0], non_blocking=True)
+            free[b].record(cur)
 
     for _ in range(min(args.warmup, 3)):
         e2e_step()
@@ -306,6 +329,10 @@ def run_ours(args) -> None:
         job_flops = float(fl[0])
     else:
         job_flops = float(total_flops)
+
+    ffn = None
+    if not args.no_extras:
+        ffn = ffn_stack_section(dev, rank, world, dist)
 
     if rank != 0:
         if dist is not None:
@@ -344,11 +371,12 @@ def run_ours(args) -> None:
                "sample": "1 of %d instances, median of 8 runs after 2 warm-ups; torch.sparse.sampled_addmm + torch.sparse.mm fp32, int32 CSR" % INSTANCES,
                "ms_per_instance": med * 1e3}
 
-    fused_layer = None
+    fused_layer = other = None
     if world == 1 and not args.no_extras:
-        del dinst, host, host_out
+        del dinst, host, host_out, slots
         torch.cuda.empty_cache()
         fused_layer = fused_layer_section(dev)
+        other = other_configs_section(dev)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -358,7 +386,7 @@ def run_ours(args) -> None:
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps},
         "gpu_launches": args.steps * INSTANCES * 2, "clocks": clocks, "kernels": kernels,
-        "fused_layer": fused_layer,
+        "fused_layer": fused_layer, "other_configs": other, "ffn_stack": ffn,
     }
     print(json.dumps(line))
     if dist is not None:
@@ -469,16 +497,214 @@ def fused_layer_section(dev, iters: int = 20, warmup: int = 5) -> dict:
     return out
 
 
+# ----------------------------------------------------------------------------------------
+# Extra section: configurations 1, 3 and 5 (single GPU) and the sharded FFN stack (N GPUs)
+# ----------------------------------------------------------------------------------------
+
+def _time_us(fn, iters=20, warmup=4):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3
+
+
+def other_configs_section(dev) -> dict:
+    """Configurations 1 and 3 (small SpMMs: cold single launch and warm rotation over > L2)."""
+    from intrasm_engine_b200 import _lib, synthetic as syn
+    st = torch.cuda.current_stream().cuda_stream
+    peak, _ = measured_peak_gbs()
+
+    def up(z):
+        return torch.as_tensor(np.ascontiguousarray(z)).to(dev)
+
+    out = {}
+    # ---- config 1: fp32 1024x1024 @90 % x 1024x256
+    a, b = syn.spmm_fp32_case(0)
+    copies = 64  # 64 x 3 MB > L2
+    cs = [(up(a.row_indices), up(a.values).clone(), up(a.row_offsets), up(a.column_indices), up(b).clone(),
+           torch.empty((1024, 256), device=dev)) for _ in range(copies)]
+
+    def c1(i):
+        ri, va, ro, ci, bb, o = cs[i % copies]
+        _lib.call("iex_spmm_f32", 1024, 1024, 256, a.nnz, ri.data_ptr(), va.data_ptr(), 0, ro.data_ptr(),
+                  ci.data_ptr(), bb.data_ptr(), None, o.data_ptr(), 1, 0, st)
+
+    us = _time_us(c1, iters=128, warmup=64)
+    by = syn.spmm_bytes(1024, 1024, 256, a.nnz, 4, 4)
+    out["cfg1_spmm_fp32"] = {"us_per_launch_rotating": us, "gflops": syn.spmm_flops(a.nnz, 256) / us / 1e3,
+                             "frac_hbm": by / us / 1e3 / peak, "bytes": by}
+    # ---- config 3: three points of the fp16 sweep (int16 indices)
+    sweep = {}
+    for rows, cols, sparsity, n in ((512, 512, 0.9, 256), (2048, 512, 0.7, 128), (512, 2048, 0.95, 128)):
+        a3, b3 = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n)
+        copies3 = 48
+        c3s = [(up(a3.row_indices), up(a3.values).clone(), up(a3.row_offsets), up(a3.column_indices),
+                up(b3).clone(), torch.empty((rows, n), dtype=torch.float16, device=dev)) for _ in range(copies3)]
+
+        def simt(i):
+            ri, va, ro, ci, bb, o = c3s[i % copies3]
+            _lib.call("iex_spmm_f16_i16", rows, cols, n, a3.nnz, ri.data_ptr(), va.data_ptr(), ro.data_ptr(),
+                      ci.data_ptr(), bb.data_ptr(), None, o.data_ptr(), 1, st)
+
+        def tc(i):
+            ri, va, ro, ci, bb, o = c3s[i % copies3]
+            _lib.call("iex_spmm_f16_tc", rows, cols, n, a3.nnz, ro.data_ptr(), ci.data_ptr(), 16, va.data_ptr(),
+                      bb.data_ptr(), o.data_ptr(), st)
+
+        by3 = syn.spmm_bytes(rows, cols, n, a3.nnz, 2, 2)
+        entry = {"nnz": a3.nnz, "bytes": by3, "cuda_core_us": _time_us(simt, iters=96, warmup=48)}
+        if n <= 128:
+            entry["tensor_core_us"] = _time_us(tc, iters=96, warmup=48)
+        best = min(v for k2, v in entry.items() if k2.endswith("_us"))
+        entry["gflops_best"] = syn.spmm_flops(a3.nnz, n) / best / 1e3
+        entry["frac_hbm_best"] = by3 / best / 1e3 / peak
+        sweep[f"{rows}x{cols}_s{sparsity}_n{n}"] = entry
+    out["cfg3_spmm_fp16_sweep"] = sweep
+    return out
+
+
+def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dict:
+    """Configuration 5: 32 ReLU-sparse FFN down projections, fp16, 256 tokens.  The activation
+    CSR (256x11008, 90 % zeros) is replicated; W_down (11008x4096) is sharded by columns over
+    the ranks; each layer all-gathers the [256, 4096/G] outputs with NCCL.  The local product
+    expands the activation CSR to a dense [256, 11008] tile operand and runs the tensor-core
+    linear on this rank's slab (stored [4096/G, 11008], K-major)."""
+    from intrasm_engine_b200 import _lib, synthetic as syn
+    from intrasm_engine_b200.pytorch.distributed import all_gather_columns
+    tokens, k, n = 256, 11008, 4096
+    n_local = n // world
+    st = torch.cuda.current_stream().cuda_stream
+    slabs = 4  # distinct weight slabs rotating (4 x 90 MB / G), so weights stream from HBM
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    w = [(torch.randn((n_local, k), generator=gen, device=dev) * 0.02).half() for _ in range(slabs)]
+    acts = []
+    for layer in range(4):
+        a, _ = syn.relu_ffn_layer_case(0, layer, tokens, k, n, with_weight=False)
+        acts.append((torch.as_tensor(a.values).to(dev), torch.as_tensor(a.row_offsets).to(dev),
+                     torch.as_tensor(a.column_indices).to(dev), a.nnz))
+    tiles = (n_local + 127) // 128
+    parts = 1 if tiles >= 24 else max(1, min(16, 148 // tiles))
+    need = _lib.lib.iex_tc_workspace_bytes(0, 1, n_local, parts, tokens)
+    ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
+    out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)
+    dense = torch.empty((tokens, k), dtype=torch.float16, device=dev)
+
+    def layer_fn(i, gather=True):
+        vals, ro, ci, _nnz = acts[i % 4]
+        _lib.call("iex_csr_to_dense_f16", tokens, k, ro.data_ptr(), ci.data_ptr(), 32, vals.data_ptr(),
+                  dense.data_ptr(), st)
+        _lib.call("iex_linear_f16_splitk", tokens, k, n_local, dense.data_ptr(), w[i % slabs].data_ptr(),
+                  out_local.data_ptr(), parts, ws.data_ptr(), ws.numel(), st)
+        return all_gather_columns(out_local) if (gather and world > 1) else out_local
+
+    def stack(gather=True):
+        for i in range(layers):
+            layer_fn(i, gather)
+
+    for _ in range(2):
+        stack()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        stack()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    e0.record()
+    for _ in range(reps):
+        stack(gather=False)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_nogather = e0.elapsed_time(e1) / reps
+    if dist is not None:
+        tt = torch.tensor([ms, ms_nogather], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_nogather = float(tt[0]), float(tt[1])
+    nnz = acts[0][3]
+    peak, _ = measured_peak_gbs()
+    by = nnz * 6 + 4 * (tokens + 1) + 4 * tokens + k * n_local * 2 + tokens * n_local * 2
+    return {"workload": "cfg5: 32 x (act 256x11008 CSR@90% x W_down 11008x4096 fp16), W_down column-sharded",
+            "layers": layers, "gpus": world, "split_k_parts": parts, "us_per_layer": ms / layers * 1e3,
+            "us_per_layer_without_allgather": ms_nogather / layers * 1e3,
+            "useful_gflops": 2.0 * nnz * n / (ms / layers * 1e-3) / 1e9,
+            "bytes_per_layer_per_gpu": by, "frac_hbm_per_gpu": by / (ms_nogather / layers * 1e-3) / 1e9 / peak}
+
+
+def profile_kernel(which: str) -> None:
+    """A few launches of one kernel on its benchmark workload, for profiler captures:
+    ``ncu ... python bench.py --profile-kernel spmm_tc``.  Prints nothing but 'done'."""
+    import intrasm_engine_b200  # noqa: F401
+    from intrasm_engine_b200 import _lib, synthetic as syn
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def up(z):
+        return torch.as_tensor(np.ascontiguousarray(z)).to(dev)
+
+    if which in ("sddmm", "spmm"):
+        runs = []
+        for i in range(12):  # 12 x 11 MB > L2
+            mask, q, k, v = syn.sddmm_chain_case(i, M, N_COLS, K_DIM, DENSITY)
+            runs.append((mask.nnz, up(mask.row_indices), up(mask.row_offsets), up(mask.column_indices), up(q),
+                         up(k), up(v), torch.empty(mask.nnz, device=dev), torch.empty((M, K_DIM), device=dev)))
+        for _ in range(2):
+            for nnz, ri, ro, ci, q, k, v, sc, o in runs:
+                if which == "sddmm":
+                    _lib.call("iex_sddmm_f32", M, K_DIM, N_COLS, nnz, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(),
+                              q.data_ptr(), k.data_ptr(), sc.data_ptr(), 1, 0, st)
+                else:
+                    _lib.call("iex_spmm_f32", M, N_COLS, K_DIM, nnz, ri.data_ptr(), sc.data_ptr(), 0, ro.data_ptr(),
+                              ci.data_ptr(), v.data_ptr(), None, o.data_ptr(), 1, 0, st)
+    else:
+        MS, MD, K, N = 11008, 12288, 4096, 64
+        a, w, x = syn.fused_layer_case(0, MS, K, N, MD)
+        cs = [dict(ro=up(a.row_offsets), ci=up(a.column_indices), va=up(a.values), w=up(w), x=up(x),
+                   xt=up(np.ascontiguousarray(x.T)), os=torch.empty((MS, N), dtype=torch.float16, device=dev),
+                   od=torch.empty((N, MD), dtype=torch.float16, device=dev)) for _ in range(2)]
+        for i in range(4):
+            c = cs[i % 2]
+            if which == "linear":
+                _lib.call("iex_linear_f16", N, K, MD, c["xt"].data_ptr(), c["w"].data_ptr(), c["od"].data_ptr(), st)
+            elif which == "spmm_tc":
+                _lib.call("iex_spmm_f16_tc", MS, K, N, a.nnz, c["ro"].data_ptr(), c["ci"].data_ptr(), 16,
+                          c["va"].data_ptr(), c["x"].data_ptr(), c["os"].data_ptr(), st)
+            elif which == "fused":
+                _lib.call("iex_fused_spmm_linear_f16", MS, MD, K, N, a.nnz, c["ro"].data_ptr(), c["ci"].data_ptr(),
+                          16, c["va"].data_ptr(), c["w"].data_ptr(), c["x"].data_ptr(), c["os"].data_ptr(),
+                          c["od"].data_ptr(), 1, st)
+            else:
+                raise SystemExit(f"unknown kernel {which}")
+    torch.cuda.synchronize()
+    assert _lib.lib.iex_last_device_status(1) == 0
+    print("done")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-kernel", default=None,
+                    choices=["sddmm", "spmm", "linear", "spmm_tc", "fused"],
+                    help="run a few launches of one kernel on its benchmark workload and exit")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the fused-layer section (used for profiler captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_kernel:
+        profile_kernel(args.profile_kernel)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

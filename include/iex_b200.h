@@ -182,6 +182,13 @@ IEX_API int iex_linear_f16_splitk_static(int tokens, int in_features, int out_fe
                                          const void* input, const void* weight, void* out,
                                          int parts, void* stream);
 
+/* Dense fp16 copy of a CSR matrix: out [m, k] row-major, zeros where nothing is stored.
+ * The device-side counterpart of the CSR <-> dense conversions the reference delegates to
+ * xformers (intrasm_engine/pytorch/utils.py:143-153); used to hand an activation CSR to the
+ * tensor-core linear as its dense tile operand.  index_bits is 16 or 32. */
+IEX_API int iex_csr_to_dense_f16(int m, int k, const int32_t* row_offsets, const void* column_indices,
+                                 int index_bits, const void* values, void* out, void* stream);
+
 /* Last device-side failure recorded by any kernel of this library (0 = none).
  * Synchronises the device.  clear != 0 resets the word. */
 IEX_API int iex_last_device_status(int clear);

@@ -52,6 +52,8 @@ SIGNATURES = {
     "iex_static_workspace_capacity": (c_size, []),
     # tokens in_features out_features input weight out parts stream
     "iex_linear_f16_splitk_static": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    # m k row_offsets cols index_bits values out stream
+    "iex_csr_to_dense_f16": (c_int, [c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)
     "iex_graph_create": (c_ptr, []),

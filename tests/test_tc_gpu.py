@@ -237,3 +237,14 @@ def test_spmm_tc_and_fused_splitk(oracle, parts):
     assert torch.equal(out_s, first)  # parts are added in part order: same bits in either launch
     assert G.close(out_d.cpu().numpy(), ref_d, RTOL, RTOL)
     _status_clean()
+
+
+@pytest.mark.parametrize("m,k,idx", [(256, 11008, np.int32), (33, 100, np.int16), (5, 7, np.int32)])
+def test_csr_to_dense(m, k, idx):
+    rng = np.random.default_rng(m + k)
+    a = syn.csr_from_mask(rng.random((m, k)) < 0.1, rng=rng, std=1.0, dtype=np.float16, index_dtype=idx)
+    da = G.DevCSR(a)
+    out = torch.full((m, k), 7.0, dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_csr_to_dense_f16", m, k, da.row_offsets.data_ptr(), G.ptr(da.column_indices),
+              16 if idx == np.int16 else 32, G.ptr(da.values), out.data_ptr(), G.stream_ptr())
+    np.testing.assert_array_equal(out.cpu().numpy(), a.to_dense())
