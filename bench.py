@@ -589,7 +589,9 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
         acts.append((torch.as_tensor(a.values).to(dev), torch.as_tensor(a.row_offsets).to(dev),
                      torch.as_tensor(a.column_indices).to(dev), a.nnz))
     tiles = (n_local + 127) // 128
-    parts = 1 if tiles >= 24 else max(1, min(16, 148 // tiles))
+    # Split-K only buys something when a rank has few tiles (its slab is narrow): with 32
+    # tiles the kernel is bound by L2 re-reads of the activation operand, not by SM count.
+    parts = max(1, 32 // tiles)
     need = _lib.lib.iex_tc_workspace_bytes(0, 1, n_local, parts, tokens)
     ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)

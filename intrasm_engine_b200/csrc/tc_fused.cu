@@ -464,7 +464,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       __half* out = sparse ? prm.s_out : prm.d_out;
       const long long sm = sparse ? static_cast<long long>(n) : prm.d_stride_m;
       const long long sn = sparse ? 1ll : prm.d_stride_n;
-      // partial tiles of this output tile: [part][128 rows][n] fp32
+      // partial tiles of this output tile: [part][n columns][128 rows] fp32
       float* part_base = prm.partials == nullptr ? nullptr
           : prm.partials + (static_cast<size_t>(sparse ? tile * prm.s_parts
                                                         : prm.s_tiles * prm.s_parts + tile * prm.d_parts)) *
@@ -479,12 +479,12 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           if (lane == 0) mbar_arrive(accum_empty);
         }
         if (un.parts > 1) {
-          float4* dst = reinterpret_cast<float4*>(
-              part_base + (static_cast<size_t>(un.part) * BM + row_local) * n + c0);
+          // partial tile stored column-major ([n][128]): the 32 lanes of a warp hold 32
+          // consecutive rows, so every store below is one coalesced 128-byte line
+          float* dst = part_base + static_cast<size_t>(un.part) * BM * n + static_cast<size_t>(c0) * BM +
+                       row_local;
 #pragma unroll
-          for (int v = 0; v < 8; ++v)
-            dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                                 __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+          for (int i = 0; i < 32; ++i) dst[i * BM] = __uint_as_float(r[i]);
         } else if (row < rows) {
           if (sn == 1) {
             uint4* dst = reinterpret_cast<uint4*>(out + row * sm + c0);
@@ -667,8 +667,8 @@ tc_reduce_kernel(const Params prm) {
   const float* base = prm.partials +
       static_cast<size_t>(sparse ? tile * prm.s_parts : prm.s_tiles * prm.s_parts + tile * prm.d_parts) *
           part_stride;
-  const int vec_per_row = n >> 2;
-  const int total_vecs = BM * vec_per_row;
+  // Partial tiles are column-major ([n][128]); a float4 holds 4 consecutive rows of one column.
+  const int total_vecs = n * (BM / 4);
   for (int f = blockIdx.y * kReduceThreads + threadIdx.x; f < total_vecs; f += kReduceSlices * kReduceThreads) {
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     int pp = 0;
@@ -684,21 +684,20 @@ tc_reduce_kernel(const Params prm) {
       const float4 t = __ldcg(reinterpret_cast<const float4*>(base + pp * part_stride) + f);
       sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
     }
-    const int rl = f / vec_per_row, c4 = (f - rl * vec_per_row) * 4;
+    const int col = f / (BM / 4), rl = (f - col * (BM / 4)) * 4;
     const int orow = tile * BM + rl;
-    if (orow >= rows) continue;
-    if (sn == 1) {
+    const float vals4[4] = {sum.x, sum.y, sum.z, sum.w};
+    if (sm == 1 && orow + 3 < rows) {  // rows contiguous in the output: one 8-byte store
       uint2 pk;
       __half2* h = reinterpret_cast<__half2*>(&pk);
       h[0] = __floats2half2_rn(sum.x, sum.y);
       h[1] = __floats2half2_rn(sum.z, sum.w);
-      *reinterpret_cast<uint2*>(out + orow * sm + c4) = pk;
-    } else {
-      out[orow * sm + (c4 + 0) * sn] = __float2half_rn(sum.x);
-      out[orow * sm + (c4 + 1) * sn] = __float2half_rn(sum.y);
-      out[orow * sm + (c4 + 2) * sn] = __float2half_rn(sum.z);
-      out[orow * sm + (c4 + 3) * sn] = __float2half_rn(sum.w);
+      __half* dst = out + orow + col * sn;
+      if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) { *reinterpret_cast<uint2*>(dst) = pk; continue; }
     }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (orow + j < rows) out[(orow + j) * sm + col * sn] = __float2half_rn(vals4[j]);
   }
 }
 
