@@ -589,9 +589,10 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
         acts.append((torch.as_tensor(a.values).to(dev), torch.as_tensor(a.row_offsets).to(dev),
                      torch.as_tensor(a.column_indices).to(dev), a.nnz))
     tiles = (n_local + 127) // 128
-    # Split-K only buys something when a rank has few tiles (its slab is narrow): with 32
-    # tiles the kernel is bound by L2 re-reads of the activation operand, not by SM count.
-    parts = max(1, 32 // tiles)
+    # With few 128-row tiles per rank a tile-per-CTA schedule leaves most SMs idle and every
+    # CTA is bound by its own TMA pipeline (~110 GB/s); split-K spreads a tile's K range over
+    # ~128 / tiles CTAs (measured optimum: 32 tiles -> 4 parts, 16 -> 8, <= 8 -> 16).
+    parts = max(1, min(16, 128 // tiles))
     need = _lib.lib.iex_tc_workspace_bytes(0, 1, n_local, parts, tokens)
     ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)
@@ -609,25 +610,38 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
         for i in range(layers):
             layer_fn(i, gather)
 
-    for _ in range(2):
-        stack()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 3
-    e0.record()
-    for _ in range(reps):
-        stack()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / reps
-    e0.record()
-    for _ in range(reps):
-        stack(gather=False)
-    e1.record()
-    torch.cuda.synchronize()
-    ms_nogather = e0.elapsed_time(e1) / reps
+    # The stack is launch-bound when driven from Python (3-4 launches per layer), so each
+    # variant is captured once into a CUDA graph (kernels and NCCL all-gathers) and replayed.
+    def timed(gather: bool) -> float:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            nonlocal st
+            st_saved, st = st, side.cuda_stream
+            for _ in range(2):
+                stack(gather)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                stack(gather)
+            st = st_saved
+        torch.cuda.current_stream().wait_stream(side)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        reps = 5
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    ms = timed(True)
+    ms_nogather = timed(False) if world > 1 else ms
     if dist is not None:
         tt = torch.tensor([ms, ms_nogather], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)

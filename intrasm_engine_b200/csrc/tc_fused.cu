@@ -646,10 +646,9 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 }
 
 // Second pass of split-K: out tile = sum over parts (in part order) of the fp32 partial
-// tiles, converted to fp16.  grid = (split tiles, kReduceSlices): every CTA sweeps one
-// slice of a tile as a flat array of float4 (coalesced), with the loads of four parts in
-// flight per thread.
-constexpr int kReduceSlices = 8;
+// tiles, converted to fp16.  grid = (split tiles, slices) with one float4 of output per
+// thread, so the whole reduction is a handful of dependent L2 round trips deep no matter how
+// large the tile is; the loads of eight parts are in flight per thread.
 constexpr int kReduceThreads = 256;
 
 __global__ void __launch_bounds__(kReduceThreads)
@@ -669,20 +668,26 @@ tc_reduce_kernel(const Params prm) {
           part_stride;
   // Partial tiles are column-major ([n][128]); a float4 holds 4 consecutive rows of one column.
   const int total_vecs = n * (BM / 4);
-  for (int f = blockIdx.y * kReduceThreads + threadIdx.x; f < total_vecs; f += kReduceSlices * kReduceThreads) {
+  for (int f = blockIdx.y * kReduceThreads + threadIdx.x; f < total_vecs; f += gridDim.y * kReduceThreads) {
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     int pp = 0;
-    for (; pp + 4 <= parts; pp += 4) {
-      float4 t[4];
+    for (; pp + 8 <= parts; pp += 8) {
+      float4 t[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 8; ++u)
         t[u] = __ldcg(reinterpret_cast<const float4*>(base + (pp + u) * part_stride) + f);
 #pragma unroll
-      for (int u = 0; u < 4; ++u) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
+      for (int u = 0; u < 8; ++u) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
     }
-    for (; pp < parts; ++pp) {
-      const float4 t = __ldcg(reinterpret_cast<const float4*>(base + pp * part_stride) + f);
-      sum.x += t.x; sum.y += t.y; sum.z += t.z; sum.w += t.w;
+    {
+      float4 t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        t[u] = (pp + u < parts) ? __ldcg(reinterpret_cast<const float4*>(base + (pp + u) * part_stride) + f)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (pp + u < parts) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
     }
     const int col = f / (BM / 4), rl = (f - col * (BM / 4)) * 4;
     const int orow = tile * BM + rl;
@@ -767,13 +772,14 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = smem;
   }
-  const int units = prm.d_tiles + prm.s_tiles;
+  const int units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
   const int grid = units < sm_count() * ctas_per_sm ? units : sm_count() * ctas_per_sm;
   kern<<<grid, (kFirstDecodeWarp + ND) * 32, smem, stream>>>(ta, tbd, tbs, prm);
   int st = launch_status();
   const int split_tiles = (prm.s_parts > 1 ? prm.s_tiles : 0) + (prm.d_parts > 1 ? prm.d_tiles : 0);
   if (st == 0 && split_tiles > 0) {
-    tc_reduce_kernel<<<dim3(split_tiles, kReduceSlices), kReduceThreads, 0, stream>>>(prm);
+    const int slices = (prm.n * (BM / 4) + kReduceThreads - 1) / kReduceThreads;
+    tc_reduce_kernel<<<dim3(split_tiles, slices), kReduceThreads, 0, stream>>>(prm);
     st = launch_status();
   }
   return st;
