@@ -60,13 +60,15 @@ sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
       const float* a_row = lhs + (static_cast<size_t>(z) * m + r) * k;
       const float* b_base = rhs + static_cast<size_t>(z) * n * k;
       for (int kc = 0; kc < k; kc += W * KV) {
-        const int kk = kc + sl * KV;
+        // Vector v of lane sl covers k-values [kc + v*4W + 4*sl, +4): the W lanes of one load
+        // instruction read 16*W contiguous bytes, so every fetched 32-byte sector is used whole.
+        const int kk = NV > 0 ? kc + sl * 4 : kc + sl;
         float4 a[NVV];
 #pragma unroll
         for (int v = 0; v < NVV; ++v) {
           a[v] = make_float4(0.f, 0.f, 0.f, 0.f);
           if constexpr (NV > 0) {
-            if (kk + 4 * v < k) a[v] = __ldg(reinterpret_cast<const float4*>(a_row + kk) + v);
+            if (kk + 4 * W * v < k) a[v] = __ldg(reinterpret_cast<const float4*>(a_row + kk + 4 * W * v));
           } else {
             if (kk < k) a[v].x = __ldg(a_row + kk);
           }
@@ -78,8 +80,8 @@ sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
 #pragma unroll
           for (int v = 0; v < NVV; ++v) {
             if constexpr (NV > 0) {
-              if (j < count && kk + 4 * v < k) {
-                const float4 b = __ldg(reinterpret_cast<const float4*>(b_row) + v);
+              if (j < count && kk + 4 * W * v < k) {
+                const float4 b = __ldg(reinterpret_cast<const float4*>(b_row + 4 * W * v));
                 acc[j] = ffma2(make_float2(a[v].x, a[v].y), make_float2(b.x, b.y), acc[j]);
                 acc[j] = ffma2(make_float2(a[v].z, a[v].w), make_float2(b.z, b.w), acc[j]);
               }
