@@ -355,10 +355,16 @@ def run_ours(args) -> None:
         kv["achieved_gbs"] = kv["bytes"] / (kv["ms"] * 1e-3) / 1e9
         kv["frac_of_%s_hbm" % peak_kind] = kv["achieved_gbs"] / peak
     dom = max(kernels, key=lambda kname: kernels[kname]["ms"])
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
+    # profiles/cuda_core_kernels_cfg2.md (12 rotating instances; part of an instance is still
+    # L2-resident from the kernel before it, hence below the algorithmic bytes)
+    ncu_traffic = {"sddmm_rowtile_kernel": 5.50e6, "spmm_rowgroup_kernel": 7.81e6}
     roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
                 "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[dom]["achieved_gbs"] / peak,
-                "traffic": None, "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
-                "us_per_launch": kernels[dom]["ms"] * 1e3}
+                "traffic": ncu_traffic[dom], "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
+                "us_per_launch": kernels[dom]["ms"] * 1e3,
+                "note": "gather-bound: every nonzero reads a 256-byte dense row through L1/L2 "
+                        "(214 MB per launch vs 8.8 MB of compulsory HBM traffic)"}
 
     cpu = None
     if world == 1:

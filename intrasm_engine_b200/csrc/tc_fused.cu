@@ -73,6 +73,10 @@ struct Params {
 
 __device__ int g_status = 0;  // last device-side failure (IEX_ERR_TIMEOUT) of this library
 
+// 32 KB of zeros: the TMA engine copies it over a sparse unit's A stage, so clearing the
+// stage costs the decoder warps and the load/store pipe nothing.
+__device__ __align__(128) unsigned char g_zero_stage[A_STAGE_BYTES];
+
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------------
@@ -336,6 +340,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const uint32_t accum_full = bar_base + 8u * (2 * S);
   const uint32_t accum_empty = bar_base + 8u * (2 * S + 1);
   const uint32_t tmem_slot = bar_base + 8u * (2 * S + 2);
+  auto zero_bar = [&](int s) { return bar_base + 8u * (2 * S + 4 + s); };  // stage cleared
   const uint32_t abort_slot = tmem_slot + 4u;
   // generic pointers to the two 4-byte slots
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -354,6 +359,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     for (int s = 0; s < S; ++s) {
       mbar_init(full_bar(s), 1 + ND);
       mbar_init(empty_bar(s), 1);
+      mbar_init(zero_bar(s), 1);
     }
     mbar_init(accum_full, 1);
     mbar_init(accum_empty, 4);
@@ -394,6 +400,15 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           const uint32_t a_dst = smem_base + s * stage_bytes;
           const uint32_t b_dst = a_dst + A_STAGE_BYTES;
           mbar_arrive_expect_tx(full_bar(s), b_stage_bytes + (sparse ? 0u : A_STAGE_BYTES));
+          if (sparse) {  // clear the A stage for the decoders (bulk copy of zeros, async proxy)
+            mbar_arrive_expect_tx(zero_bar(s), A_STAGE_BYTES);
+            asm volatile(
+                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(a_dst),
+                "l"(g_zero_stage), "r"(static_cast<uint32_t>(A_STAGE_BYTES)), "r"(zero_bar(s))
+                : "memory");
+          } else {
+            mbar_arrive(zero_bar(s));  // keeps the barrier's phase in step with the stage ring
+          }
           if (!sparse) {
             tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, tile * BM);
             tma_load_2d(a_dst + A_ATOM_BYTES, &tma_a, full_bar(s), kb * BK + 64, tile * BM);
@@ -525,7 +540,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const IT* cols = static_cast<const IT*>(prm.s_cols);
     const __half* vals = prm.s_values;
     const int nnz = prm.s_nnz;
-    const uint32_t ring_base = bar_base + 8u * (2 * S + 2) + 16u;  // 16-byte aligned
+    const uint32_t ring_base = bar_base + 8u * (3 * S + 4) + ((S & 1) ? 8u : 0u);  // 16-byte aligned
     uint32_t it = 0;
     bool ok = true;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
@@ -559,19 +574,10 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % S;
         const uint32_t ph = (it / S) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 32)) { ok = false; break; }
         if (sparse) {
+          // the producer had the TMA engine clear this stage (after the MMAs released it)
+          if (!mbar_wait(zero_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
           const uint32_t a_base = smem_base + s * stage_bytes;
-          // zero this warp's rows of both atoms (rows are 128 B apart: contiguous)
-          constexpr int kZeroVecs = kRowsPerWarp * 128 / 16 / 32;  // uint4 per lane per atom
-#pragma unroll
-          for (int a = 0; a < 2; ++a)
-#pragma unroll
-            for (int v = 0; v < kZeroVecs; ++v) {
-              const uint32_t addr =
-                  a_base + a * A_ATOM_BYTES + dw * kRowsPerWarp * 128 + (v * 32 + lane) * 16;
-              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(addr), "r"(0u) : "memory");
-            }
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t kbeg = static_cast<uint32_t>(kb * BK + h * 64);
@@ -623,6 +629,8 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             asm volatile("cp.async.commit_group;" ::: "memory");
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        } else {
+          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 32)) { ok = false; break; }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
@@ -763,7 +771,7 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
   prm.num_stages = stages;
   const size_t ring = ND > 0 ? static_cast<size_t>(BM) * kRing * (2 + sizeof(IT)) : 0;
   const size_t smem = 1024 + static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256) +
-                      8 * (2 * stages + 2) + 32 + ring;
+                      8 * (3 * stages + 4) + 32 + ring;
   auto kern = tc_units_kernel<ND, IT>;
   static size_t configured = 0;
   if (smem > configured) {
