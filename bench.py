@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (``config.workload``): benchmark configuration 2 of BASELINE.json — fp32 SDDMM
+Workload (``config.workload``): benchmark configuration 2 (of five) — fp32 SDDMM
 over a 4096x4096 mask at 95 % sparsity (K = 64) followed by the SpMM of that CSR with V
 (4096x64).  One STEP is one pass of that chain over a batch of ``instances`` independent
 seeded instances whose combined inputs exceed the 126 MB L2, so every launch streams its

@@ -5,7 +5,11 @@ library exists) compiles every ``csrc/*.cu`` to an object file
 under ``build/`` (one nvcc process per file, in parallel) and links them into
 ``intrasm_engine_b200/libiex_b200.so``.  The CUDA runtime is linked statically, so the
 library has no load-time dependency besides libc/libstdc++ and the driver.
-``CMakeLists.txt`` beside this file describes the same build for CMake users.
+It then compiles ``torch_ext/iex_torch_ext.cpp`` with g++ against the installed torch
+headers into ``intrasm_engine_b200/libiex_torch_ext.so``, the extension that registers
+``torch.ops.iex_ops`` and calls the C ABI (it finds ``libiex_b200.so`` beside itself through
+an ``$ORIGIN`` run path).  ``CMakeLists.txt`` beside this file describes the C-ABI build for
+CMake users.
 """
 from __future__ import annotations
 
@@ -20,6 +24,8 @@ REPO_DIR = os.path.dirname(PKG_DIR)
 CSRC = os.path.join(PKG_DIR, "csrc")
 OBJ_DIR = os.path.join(REPO_DIR, "build", "iex_b200")
 LIB_PATH = os.path.join(PKG_DIR, "libiex_b200.so")
+EXT_SRC = os.path.join(PKG_DIR, "torch_ext", "iex_torch_ext.cpp")
+EXT_PATH = os.path.join(PKG_DIR, "libiex_torch_ext.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -66,8 +72,38 @@ def _compile(src: str, verbose: bool) -> str:
     return obj
 
 
+def _cuda_include() -> str:
+    return os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+
+
+def build_torch_ext(force: bool = False) -> str:
+    """Compile the torch extension that registers ``torch.ops.iex_ops``; returns its path."""
+    newest = max(os.path.getmtime(EXT_SRC), os.path.getmtime(LIB_PATH), os.path.getmtime(__file__),
+                 os.path.getmtime(os.path.join(REPO_DIR, "include", "iex_b200.h")))
+    if not force and os.path.exists(EXT_PATH) and os.path.getmtime(EXT_PATH) >= newest:
+        return EXT_PATH
+    import torch
+    torch_dir = os.path.dirname(torch.__file__)
+    torch_lib = os.path.join(torch_dir, "lib")
+    torch_inc = os.path.join(torch_dir, "include")
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+           "-I", os.path.join(REPO_DIR, "include"),
+           "-I", torch_inc, "-I", os.path.join(torch_inc, "torch", "csrc", "api", "include"),
+           "-I", _cuda_include(),
+           EXT_SRC, "-o", EXT_PATH,
+           "-L", PKG_DIR, "-liex_b200",
+           "-L", torch_lib, "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+           "-Wl,-rpath,$ORIGIN"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"torch extension build failed:\n{res.stdout}\n{res.stderr}")
+    return EXT_PATH
+
+
 def build(verbose: bool = False, force: bool = False) -> str:
-    """Compile and link the library; returns its path.  Up-to-date objects are reused."""
+    """Compile and link the library and the torch extension; returns the library's path.
+    Up-to-date objects are reused."""
     os.makedirs(OBJ_DIR, exist_ok=True)
     if force:
         for f in os.listdir(OBJ_DIR):
@@ -83,6 +119,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    build_torch_ext(force)
     return LIB_PATH
 
 

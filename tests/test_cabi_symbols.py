@@ -43,11 +43,25 @@ def test_status_helpers():
 def test_ops_registered_with_reference_schemas():
     import torch
     import intrasm_engine_b200  # noqa: F401
+    from intrasm_engine_b200 import ops
     for name in ("spmm_sputnik_reuse_weight", "spmm_sputnik_atomic",
                  "spmm_sputnik_reuse_weight_half", "sddmm_sputnik_atomic_upd_weight"):
+        assert name in ops.OP_NAMES
+    for name in ops.OP_NAMES:
         assert hasattr(torch.ops.iex_ops, name)
+        # compiled registration with a CUDA kernel and no CPU kernel
+        assert torch._C._dispatch_has_kernel_for_dispatch_key(f"iex_ops::{name}", "CUDA")
+        assert not torch._C._dispatch_has_kernel_for_dispatch_key(f"iex_ops::{name}", "CPU")
     schema = str(torch.ops.iex_ops.spmm_sputnik_reuse_weight.default._schema)
     assert "Tensor b, Tensor row_indices, Tensor values, Tensor row_offsets, Tensor column_indices, int m" in schema
+
+
+def test_torch_extension_is_a_compiled_library():
+    """The operators come from a shared object in the package, not from Python functions."""
+    from intrasm_engine_b200 import ops
+    raw = ctypes.CDLL(ops.EXT_PATH)
+    assert os.path.dirname(ops.EXT_PATH) == os.path.join(REPO, "intrasm_engine_b200")
+    assert raw is not None
 
 
 def test_no_cpu_fallback():

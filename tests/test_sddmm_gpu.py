@@ -60,7 +60,7 @@ def test_sddmm_accumulate_and_determinism(oracle):
 
 
 def test_sddmm_cfg2_chain_full_size(oracle):
-    """BASELINE config 2: SDDMM over a 4096x4096 mask at 95 % sparsity (K=64), then SpMM with V."""
+    """Benchmark configuration 2: SDDMM over a 4096x4096 mask at 95 % sparsity (K=64), then SpMM with V."""
     mask, q, k, v = syn.sddmm_chain_case(0)
     dm = G.DevCSR(mask)
     scores = G.sddmm_f32(dm, G.dev(q)[None], G.dev(k)[None])

@@ -129,7 +129,7 @@ def test_spmm_f32_bias_relu_accumulate_batch(oracle):
 
 
 def test_spmm_cfg1_full_size(oracle):
-    """BASELINE config 1: 1024x1024 at 90 % sparsity times 1024x256, fp32."""
+    """Benchmark configuration 1: 1024x1024 at 90 % sparsity times 1024x256, fp32."""
     for seed in (0, 1):
         a, b = syn.spmm_fp32_case(seed)
         got = G.spmm_f32(G.DevCSR(a), G.dev(b)[None])[0].cpu().numpy()
@@ -143,7 +143,7 @@ def test_spmm_cfg1_full_size(oracle):
 @pytest.mark.parametrize("sparsity", [0.5, 0.9, 0.98])
 @pytest.mark.parametrize("n", [128, 256])
 def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n):
-    """BASELINE config 3 (subset of the sweep): fp16 values, fp32 accumulate, int16 indices."""
+    """Benchmark configuration 3 (subset of the sweep): fp16 values, fp32 accumulate, int16 indices."""
     a, b = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n)
     got = G.spmm_f16(G.DevCSR(a), G.dev(b)[None])[0].cpu().numpy()
     ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, rows)[0]

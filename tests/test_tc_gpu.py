@@ -146,7 +146,7 @@ def test_fused_small(oracle, ms, md, k, n):
 
 
 def test_fused_cfg4_full_size(oracle):
-    """BASELINE config 4: W_up 11008x4096 CSR at 50 % times X 4096x64, fused with W_qkv 12288x4096."""
+    """Benchmark configuration 4: W_up 11008x4096 CSR at 50 % times X 4096x64, fused with W_qkv 12288x4096."""
     a, w, x = syn.fused_layer_case(0)
     da = G.DevCSR(a)
     out_s, out_d = _fused(da, G.dev(w), G.dev(x))
