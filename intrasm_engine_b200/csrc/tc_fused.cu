@@ -31,6 +31,7 @@
 // frees its TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -46,6 +47,10 @@ constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
 constexpr int kFirstDecodeWarp = 6;
 constexpr int kDecodeWarps = 16;          // CSR decoder warps of the sparse-capable instance
 constexpr uint32_t kSpinLimit = 1u << 23;  // mbarrier polls (with back-off) before a wait gives up
+constexpr int kMaxStages = 6;             // dense stages (barrier slots reserved)
+constexpr int kMaxASlots = 8;             // sparse A slots of 64 columns (a power of two)
+constexpr int kMaxBSlots = 4;             // sparse B slots (X rows of one 64-column block)
+constexpr int kRingGranules = 16;         // 8-nonzero granules per row ring (128 nonzeros)
 
 struct Params {
   // dense branch: out[f * d_stride_m + t * d_stride_n]
@@ -63,6 +68,11 @@ struct Params {
   int k, n;
   int num_stages, tmem_cols;
   int* status;
+  // shared-memory plan of sparse units: s_a_slots (2, 4 or 8) A slots of 16 KB at offset 0,
+  // s_b_slots (2 or 4) B slots after them, the CSR rings at s_ring_offset; mbarriers at
+  // bar_offset (past the larger of the dense and the sparse plan, which overlay each other)
+  int s_a_slots, s_b_slots;
+  uint32_t s_ring_offset, bar_offset;
   // split-K: every tile's K range is cut into `parts` equal runs of k-blocks, one unit
   // each.  With parts > 1 a unit writes its fp32 partial tile to `partials`
   // ([tile][part][128][n], sparse tiles first) and a second, tiny kernel adds the parts in
@@ -72,10 +82,6 @@ struct Params {
 };
 
 __device__ int g_status = 0;  // last device-side failure (IEX_ERR_TIMEOUT) of this library
-
-// 32 KB of zeros: the TMA engine copies it over a sparse unit's A stage, so clearing the
-// stage costs the decoder warps and the load/store pipe nothing.
-__device__ __align__(128) unsigned char g_zero_stage[A_STAGE_BYTES];
 
 // ---------------------------------------------------------------------------------------
 // PTX wrappers
@@ -98,6 +104,17 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {  // never suspends
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -208,20 +225,19 @@ __device__ __forceinline__ void window_kill(Window<uint16_t>& w, int e) {
 }
 __device__ __forceinline__ void window_kill(Window<int>& w, int e) { w.c[e] = 0xffffffffu; }
 
-// Ring staging of the CSR stream.  Every row of the tile has a ring of kRing nonzeros
-// (values and indices) in shared memory, addressed by position modulo kRing, that is
-// kept filled up to kRing positions past the row's cursor with 16-byte cp.async copies
-// ("granules" of 8 nonzeros).  Granules may start before the row or run past its end;
-// what they hold there is masked when a window is read.
-constexpr int kRing = 128;            // nonzeros per row ring
-constexpr int kRingGranules = kRing / 8;
+// Ring staging of the CSR stream.  Every row of the tile has a ring of 128 nonzeros
+// (values and indices; kRingGranules "granules" of 8 nonzeros) in shared memory, addressed
+// by position modulo the ring size, that is kept filled up to one ring size past the row's
+// cursor with 16-byte cp.async copies.  Granules may start before the row or run past its
+// end; what they hold there is masked when a window is read.
 
 template <typename IT>
 __device__ __forceinline__ void ring_issue(uint32_t vring, uint32_t cring, const __half* __restrict__ vals,
-                                           const IT* __restrict__ cols, int g, int rend, int nnz) {
+                                           const IT* __restrict__ cols, int g, int rend, int nnz,
+                                           uint32_t rg_mask) {
   const int p = g * 8;
   if (p >= rend) return;  // nothing of this row there
-  const uint32_t slot = static_cast<uint32_t>(g) & (kRingGranules - 1);
+  const uint32_t slot = static_cast<uint32_t>(g) & rg_mask;
   const uint32_t vdst = vring + slot * 16u;
   const uint32_t cdst = cring + slot * static_cast<uint32_t>(8 * sizeof(IT));
   if (p + 8 <= nnz) {
@@ -245,20 +261,20 @@ __device__ __forceinline__ void ring_issue(uint32_t vring, uint32_t cring, const
   }
 }
 
-// Reads nonzeros [my, my + 8) (my a multiple of 8) from the ring.  Positions outside the
-// row [rstart, rend) get an index that no k-block matches, so that the scatter loop needs a
-// single unsigned compare per nonzero.  Positions inside the row but before the cursor
-// hold columns of earlier k-blocks and fail that compare by themselves.
+// Reads nonzeros [my, my + 8) (my a multiple of 8) from the ring.  Positions outside
+// [lo, rend) -- before the row's cursor or past the row's end -- get the largest index,
+// which no open column range contains, so that the scatter loop needs a single unsigned
+// compare per nonzero.
 template <typename IT>
 __device__ __forceinline__ void ring_read(Window<IT>& w, uint32_t vring, uint32_t cring, int my,
-                                          int rstart, int rend) {
+                                          int lo, int rend, uint32_t rg_mask) {
   constexpr int kC = 8 * sizeof(IT) / 4;
   if (my >= rend) {
 #pragma unroll
     for (int e = 0; e < kC; ++e) w.c[e] = 0xffffffffu;
     return;
   }
-  const uint32_t slot = static_cast<uint32_t>(my >> 3) & (kRingGranules - 1);
+  const uint32_t slot = static_cast<uint32_t>(my >> 3) & rg_mask;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(w.v[0]), "=r"(w.v[1]), "=r"(w.v[2]), "=r"(w.v[3])
                : "r"(vring + slot * 16u));
@@ -267,33 +283,37 @@ __device__ __forceinline__ void ring_read(Window<IT>& w, uint32_t vring, uint32_
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(w.c[4 * q]), "=r"(w.c[4 * q + 1]), "=r"(w.c[4 * q + 2]), "=r"(w.c[4 * q + 3])
                  : "r"(cring + slot * static_cast<uint32_t>(8 * sizeof(IT)) + 16u * q));
-  if (my + 8 > rend || my < rstart) {
+  if (my + 8 > rend || my < lo) {
 #pragma unroll
     for (int e = 0; e < 8; ++e)
-      if (my + e >= rend || my + e < rstart) window_kill(w, e);
+      if (my + e >= rend || my + e < lo) window_kill(w, e);
   }
 }
 
-// Writes the window's nonzeros whose column lies in [kbeg, kbeg + 64) into one 64-column
-// atom of the A stage.  row_swz = (address of the row inside the atom) ^ ((row & 7) << 4):
-// XOR-ing the byte column into it applies the 128-byte swizzle.  Returns how many were
-// written.
+// Writes the window's nonzeros whose column is below open_end into the A slots.  A slot is
+// one 64-column swizzle atom ([128 rows x 128 bytes]); the slots of consecutive 64-column
+// blocks lie 16 KB apart in a power-of-two ring, so the slot of a column is a bit field of
+// the column index: address = row part ^ (column-in-atom part) + (slot part).
+// row_swz = (A region + row * 128) ^ ((row & 7) << 4); XOR-ing the byte column into it
+// applies the 128-byte swizzle.  Returns how many were written.
 template <typename IT>
-__device__ __forceinline__ int scatter_window(const Window<IT>& w, uint32_t kbeg, uint32_t row_swz) {
+__device__ __forceinline__ int scatter_open(const Window<IT>& w, uint32_t open_end, uint32_t row_swz,
+                                            uint32_t slot_mask) {
   int nvalid = 0;
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
-    const uint32_t cl = window_index(w, e) - kbeg;
-    if (cl < 64u) {
+    const uint32_t c = window_index(w, e);
+    if (c < open_end) {
       const uint16_t hv = static_cast<uint16_t>((e & 1) ? (w.v[e >> 1] >> 16) : w.v[e >> 1]);
-      asm volatile("st.shared.u16 [%0], %1;" ::"r"(row_swz ^ (cl << 1)), "h"(hv) : "memory");
+      const uint32_t addr = (row_swz ^ ((c & 63u) << 1)) + ((c << 8) & slot_mask);
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
       ++nvalid;
     }
   }
   return nvalid;
 }
 // Sum over the 8 lanes of a row group (xor butterfly; all four groups of a warp at once).
-__device__ __forceinline__ int group8_sum(int v, unsigned) {
+__device__ __forceinline__ int group8_sum(int v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
   v += __shfl_xor_sync(0xffffffffu, v, 2);
   v += __shfl_xor_sync(0xffffffffu, v, 4);
@@ -331,39 +351,61 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int n = prm.n;
+  // dense units: ring of S stages, each [A 128x128 | B 128xN]
   const uint32_t b_stage_bytes = static_cast<uint32_t>(n) * 256u;
   const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
   const int S = prm.num_stages;
-  const uint32_t bar_base = smem_base + S * stage_bytes;
-  auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
-  const uint32_t accum_full = bar_base + 8u * (2 * S);
-  const uint32_t accum_empty = bar_base + 8u * (2 * S + 1);
-  const uint32_t tmem_slot = bar_base + 8u * (2 * S + 2);
-  auto zero_bar = [&](int s) { return bar_base + 8u * (2 * S + 4 + s); };  // stage cleared
-  const uint32_t abort_slot = tmem_slot + 4u;
-  // generic pointers to the two 4-byte slots
+  // sparse units: SA A slots of 64 columns, then SB B slots (X rows of a 64-column block),
+  // then the CSR rings
+  const int SA = prm.s_a_slots, SB = prm.s_b_slots;
+  const uint32_t s_b_slot_bytes = static_cast<uint32_t>(n) * 128u;
+  const uint32_t s_b_region = smem_base + static_cast<uint32_t>(SA) * A_ATOM_BYTES;
+  const uint32_t bar_base = smem_base + prm.bar_offset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                          // dense
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  // sparse: A slots are filled by the decoder warps and released by the tensor-core warp;
+  // B slots are filled by the producer's TMA loads
+  auto a_full_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + s); };
+  auto a_empty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + kMaxASlots + s); };
+  auto b_full_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxASlots + s); };
+  auto b_empty_bar = [&](int s) { return bar_base + 8u * (2 * kMaxStages + 2 * kMaxASlots + kMaxBSlots + s); };
+  constexpr uint32_t kBarCount = 2 * kMaxStages + 2 * kMaxASlots + 2 * kMaxBSlots;
+  const uint32_t accum_full = bar_base + 8u * kBarCount;
+  const uint32_t accum_empty = accum_full + 8u;
+  const uint32_t tmem_slot = accum_full + 16u;
   uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
   volatile uint32_t* tmem_ptr_generic =
-      reinterpret_cast<volatile uint32_t*>(smem_aligned + S * stage_bytes + 8u * (2 * S + 2));
+      reinterpret_cast<volatile uint32_t*>(smem_aligned + prm.bar_offset + 8u * kBarCount + 16u);
   volatile int* abort_flag =
-      reinterpret_cast<volatile int*>(smem_aligned + S * stage_bytes + 8u * (2 * S + 2) + 4u);
-  (void)abort_slot;
+      reinterpret_cast<volatile int*>(smem_aligned + prm.bar_offset + 8u * kBarCount + 20u);
+  // number of this CTA's units whose accumulator is complete (all tensor-core reads of
+  // shared memory done); written by the first epilogue warp
+  volatile uint32_t* units_done =
+      reinterpret_cast<volatile uint32_t*>(smem_aligned + prm.bar_offset + 8u * kBarCount + 24u);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int total_units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
-  const int k_blocks = (prm.k + BK - 1) / BK;
+  const int k_blocks = (prm.k + BK - 1) / BK;   // dense: 128 columns per stage
+  const int k_slots = (prm.k + 63) / 64;        // sparse: 64 columns per slot
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) {
-      mbar_init(full_bar(s), 1 + ND);
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(zero_bar(s), 1);
+    }
+    for (int s = 0; s < kMaxASlots; ++s) {
+      mbar_init(a_full_bar(s), ND > 0 ? ND : 1);
+      mbar_init(a_empty_bar(s), 1);
+    }
+    for (int s = 0; s < kMaxBSlots; ++s) {
+      mbar_init(b_full_bar(s), 1);
+      mbar_init(b_empty_bar(s), 1);
     }
     mbar_init(accum_full, 1);
     mbar_init(accum_empty, 4);
     *abort_flag = 0;
+    *units_done = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -378,47 +420,70 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_generic;
 
+  // Dense stages and sparse slots / rings overlay the same shared memory.  A role that writes
+  // shared memory for a unit whose kind differs from the CTA's previous unit first waits until
+  // the previous unit's accumulator is complete (units_done): every tensor-core read and
+  // every TMA copy of that unit has finished by then, and so have the decoders' ring copies,
+  // which have all landed before they release a unit's last slot.
+  auto wait_units_done = [&](uint32_t want) -> bool {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      if (*units_done >= want) { __threadfence_block(); return true; }
+      __nanosleep(64);
+      if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(prm.status, IEX_ERR_TIMEOUT);
+    atomicExch(&g_status, IEX_ERR_TIMEOUT);
+    return false;
+  };
+
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b_dense) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&tma_b_sparse) : "memory");
-      uint32_t it = 0;
-      bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      uint32_t it = 0, unit_it = 0, b_empty_ph = 0;
+      bool ok = true, prev_sparse = false;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
         const Unit un = unit_of(u, prm, gridDim.x);
-        const bool sparse = un.sparse;
         const int tile = un.tile;
-        const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
-        const bool b_mn = sparse || prm.d_b_mn;
-        const CUtensorMap* tmb = sparse ? &tma_b_sparse : &tma_b_dense;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
-          const uint32_t a_dst = smem_base + s * stage_bytes;
-          const uint32_t b_dst = a_dst + A_STAGE_BYTES;
-          mbar_arrive_expect_tx(full_bar(s), b_stage_bytes + (sparse ? 0u : A_STAGE_BYTES));
-          if (sparse) {  // clear the A stage for the decoders (bulk copy of zeros, async proxy)
-            mbar_arrive_expect_tx(zero_bar(s), A_STAGE_BYTES);
-            asm volatile(
-                "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(a_dst),
-                "l"(g_zero_stage), "r"(static_cast<uint32_t>(A_STAGE_BYTES)), "r"(zero_bar(s))
-                : "memory");
-          } else {
-            mbar_arrive(zero_bar(s));  // keeps the barrier's phase in step with the stage ring
+        if (unit_it > 0 && un.sparse != prev_sparse && !wait_units_done(unit_it)) { ok = false; break; }
+        prev_sparse = un.sparse;
+        if (un.sparse) {
+          const int kb0 = un.part * k_slots / un.parts, kb1 = (un.part + 1) * k_slots / un.parts;
+          for (int kb = kb0; kb < kb1; ++kb) {
+            const int s = kb & (SB - 1);
+            if (!mbar_wait(b_empty_bar(s), ((b_empty_ph >> s) & 1u) ^ 1u, abort_flag, prm.status, 64)) {
+              ok = false;
+              break;
+            }
+            b_empty_ph ^= 1u << s;
+            const uint32_t b_dst = s_b_region + s * s_b_slot_bytes;
+            mbar_arrive_expect_tx(b_full_bar(s), s_b_slot_bytes);
+            // X [K, N]: one [64 k-rows x 64 cols] box per 64 columns
+            for (int j = 0; j < n / 64; ++j)
+              tma_load_2d(b_dst + j * (64 * 128), &tma_b_sparse, b_full_bar(s), j * 64, kb * 64);
           }
-          if (!sparse) {
+        } else {
+          const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
+          const bool b_mn = prm.d_b_mn;
+          for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1u;
+            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
+            const uint32_t a_dst = smem_base + s * stage_bytes;
+            const uint32_t b_dst = a_dst + A_STAGE_BYTES;
+            mbar_arrive_expect_tx(full_bar(s), b_stage_bytes + A_STAGE_BYTES);
             tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, tile * BM);
             tma_load_2d(a_dst + A_ATOM_BYTES, &tma_a, full_bar(s), kb * BK + 64, tile * BM);
-          }
-          if (b_mn) {  // X [K, N]: one [128 k-rows x 64 cols] box per 64 columns
-            for (int j = 0; j < n / 64; ++j)
-              tma_load_2d(b_dst + j * (BK * 128), tmb, full_bar(s), j * 64, kb * BK);
-          } else {  // X^T [N, K]: two [N rows x 64 k] boxes
-            tma_load_2d(b_dst, tmb, full_bar(s), kb * BK, 0);
-            tma_load_2d(b_dst + n * 128, tmb, full_bar(s), kb * BK + 64, 0);
+            if (b_mn) {  // X [K, N]: one [128 k-rows x 64 cols] box per 64 columns
+              for (int j = 0; j < n / 64; ++j)
+                tma_load_2d(b_dst + j * (BK * 128), &tma_b_dense, full_bar(s), j * 64, kb * BK);
+            } else {  // X^T [N, K]: two [N rows x 64 k] boxes
+              tma_load_2d(b_dst, &tma_b_dense, full_bar(s), kb * BK, 0);
+              tma_load_2d(b_dst + n * 128, &tma_b_dense, full_bar(s), kb * BK + 64, 0);
+            }
           }
         }
       }
@@ -432,32 +497,54 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc_k = (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (8u << 24);
       const uint32_t idesc_mn = idesc_k | (1u << 16);
-      uint32_t it = 0, unit_it = 0;
+      uint32_t it = 0, unit_it = 0, a_full_ph = 0, b_full_ph = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
         const Unit un = unit_of(u, prm, gridDim.x);
-        const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
-        const bool b_mn = un.sparse || prm.d_b_mn;
-        const uint32_t idesc = b_mn ? idesc_mn : idesc_k;
         if (!mbar_wait(accum_empty, (unit_it & 1u) ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
         tcgen05_fence_after();
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % S;
-          const uint32_t ph = (it / S) & 1u;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
-          tcgen05_fence_after();
-          const uint32_t a_base = smem_base + s * stage_bytes;
-          const uint32_t b_base = a_base + A_STAGE_BYTES;
+        if (un.sparse) {
+          const int kb0 = un.part * k_slots / un.parts, kb1 = (un.part + 1) * k_slots / un.parts;
+          for (int kb = kb0; kb < kb1; ++kb) {
+            const int sa = kb & (SA - 1), sb = kb & (SB - 1);
+            if (!mbar_wait(b_full_bar(sb), (b_full_ph >> sb) & 1u, abort_flag, prm.status, 32)) { ok = false; break; }
+            b_full_ph ^= 1u << sb;
+            if (!mbar_wait(a_full_bar(sa), (a_full_ph >> sa) & 1u, abort_flag, prm.status, 32)) { ok = false; break; }
+            a_full_ph ^= 1u << sa;
+            tcgen05_fence_after();
+            const uint32_t a_base = smem_base + sa * A_ATOM_BYTES;
+            const uint32_t b_base = s_b_region + sb * s_b_slot_bytes;
 #pragma unroll
-          for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-            const uint64_t adesc =
-                smem_desc(a_base + (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32, 16, 1024);
-            const uint64_t bdesc =
-                b_mn ? smem_desc(b_base + ks * (UMMA_K * 128), BK * 128, 1024)
-                     : smem_desc(b_base + (ks >> 2) * (n * 128) + (ks & 3) * 32, 16, 1024);
-            umma_f16(tmem_base, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
+            for (int ks = 0; ks < 64 / UMMA_K; ++ks) {
+              const uint64_t adesc = smem_desc(a_base + ks * 32, 16, 1024);
+              const uint64_t bdesc = smem_desc(b_base + ks * (UMMA_K * 128), 64 * 128, 1024);
+              umma_f16(tmem_base, adesc, bdesc, idesc_mn, (kb != kb0 || ks != 0) ? 1u : 0u);
+            }
+            umma_commit(a_empty_bar(sa));
+            umma_commit(b_empty_bar(sb));
           }
-          umma_commit(empty_bar(s));
+        } else {
+          const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
+          const bool b_mn = prm.d_b_mn;
+          const uint32_t idesc = b_mn ? idesc_mn : idesc_k;
+          for (int kb = kb0; kb < kb1; ++kb, ++it) {
+            const int s = it % S;
+            const uint32_t ph = (it / S) & 1u;
+            if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
+            tcgen05_fence_after();
+            const uint32_t a_base = smem_base + s * stage_bytes;
+            const uint32_t b_base = a_base + A_STAGE_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
+              const uint64_t adesc =
+                  smem_desc(a_base + (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32, 16, 1024);
+              const uint64_t bdesc =
+                  b_mn ? smem_desc(b_base + ks * (UMMA_K * 128), BK * 128, 1024)
+                       : smem_desc(b_base + (ks >> 2) * (n * 128) + (ks & 3) * 32, 16, 1024);
+              umma_f16(tmem_base, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
+            }
+            umma_commit(empty_bar(s));
+          }
         }
         if (ok) umma_commit(accum_full);
       }
@@ -473,6 +560,10 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const int tile = un.tile;
       if (!mbar_wait(accum_full, unit_it & 1u, abort_flag, prm.status, 256)) { ok = false; break; }
       tcgen05_fence_after();
+      if (warp == 2 && lane == 0) {
+        __threadfence_block();
+        *units_done = unit_it + 1u;
+      }
       const int row_local = q * 32 + lane;
       const int row = tile * BM + row_local;
       const int rows = sparse ? prm.s_m : prm.d_m;
@@ -524,12 +615,16 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   } else if (ND > 0) {
     // ------------------------------------------------------------------ CSR decoders
     // Each warp owns kRowsPerWarp rows of the tile; a group of 8 lanes works on one row,
-    // four rows per pass.  A stage (128 columns) is filled as two 64-column halves, one
-    // swizzle atom each.  A row's nonzeros for one half are a contiguous run that starts
-    // at the row's cursor; the run is read from the row's shared-memory ring as a window
-    // of 64 nonzeros at [base, base+64), base = cursor rounded down to 8 (a second window
-    // when the run is longer).  After each half the ring is topped up to kRing positions
-    // past the new cursor, so global-memory latency is several halves away from use.
+    // four rows per pass.  The rows are decoded as a data flow: in every round a row group
+    // reads the next 64 nonzeros of its row (a "window", from the row's shared-memory ring)
+    // and writes those whose column lies below the end of the open slots -- wherever they
+    // fall among these -- so no nonzero is read twice except where a window is cut at that
+    // end.  Open slots are the ones the tensor-core warp is done with (the warp then clears
+    // its own rows of the slot) and this warp has not yet released.  A warp releases slot j (arrives on its full barrier) once every one of its
+    // rows has moved past column 64 * (j + 1); the tensor-core warp consumes a slot when all
+    // decoder warps have released it and X's rows for it have landed.
+    // After each round the ring is topped up to one ring size past the new cursor, so
+    // global-memory latency is a round away from use.
     constexpr int kNd = ND > 0 ? ND : 1;
     constexpr int kRowsPerWarp = BM / kNd;
     constexpr int kIters = kRowsPerWarp / 4;
@@ -540,105 +635,115 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const IT* cols = static_cast<const IT*>(prm.s_cols);
     const __half* vals = prm.s_values;
     const int nnz = prm.s_nnz;
-    const uint32_t ring_base = bar_base + 8u * (3 * S + 4) + ((S & 1) ? 8u : 0u);  // 16-byte aligned
-    uint32_t it = 0;
-    bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+    const uint32_t ring_base = smem_base + prm.s_ring_offset;  // 16-byte aligned
+    constexpr int rg = kRingGranules;
+    constexpr uint32_t rg_mask = static_cast<uint32_t>(rg - 1);
+    const uint32_t slot_mask = static_cast<uint32_t>(SA - 1) << 14;
+    uint32_t unit_it = 0, a_empty_ph = 0;
+    bool ok = true, prev_sparse = false;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
       const Unit un = unit_of(u, prm, gridDim.x);
-      const bool sparse = un.sparse;
+      if (!un.sparse) { prev_sparse = false; continue; }
       const int tile = un.tile;
-      const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
-      int cur[kIters], rend[kIters], rstart[kIters], filled[kIters];
-      uint32_t vring[kIters], cring[kIters];
-      if (sparse) {
+      const int kb0 = un.part * k_slots / un.parts, kb1 = (un.part + 1) * k_slots / un.parts;
+      // the rings overlay the stages of a dense unit before this one
+      if (unit_it > 0 && !prev_sparse && !wait_units_done(unit_it)) { ok = false; break; }
+      prev_sparse = true;
+      int cur[kIters], rend[kIters], filled[kIters];
+      uint32_t vring[kIters], cring[kIters], row_swz[kIters];
+#pragma unroll
+      for (int i = 0; i < kIters; ++i) {
+        const int row_local = dw * kRowsPerWarp + i * 4 + grp;
+        const int row = tile * BM + row_local;
+        const bool in = row < prm.s_m;
+        const int rstart = in ? __ldg(prm.s_row_offsets + row) : 0;
+        rend[i] = in ? __ldg(prm.s_row_offsets + row + 1) : 0;
+        cur[i] = rstart;
+        if (kb0 > 0)  // this part starts inside the row: first nonzero with column >= kb0 * 64
+          cur[i] = group_lower_bound<IT>(cols, rstart, rend[i], kb0 * 64, sl, gmask);
+        vring[i] = ring_base + row_local * (rg * 16u);
+        cring[i] = ring_base + BM * (rg * 16u) + row_local * (rg * 8u * static_cast<uint32_t>(sizeof(IT)));
+        row_swz[i] = (smem_base + row_local * 128) ^ (static_cast<uint32_t>(row_local & 7) << 4);
+        const int g0 = cur[i] >> 3;
+        for (int j = 0; j < rg; j += 8)
+          ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + j + sl, rend[i], nnz, rg_mask);
+        filled[i] = g0 + rg;
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.commit_group;" ::: "memory");  // so that wait_group 1 covers the fill
+      int lo = kb0, hi = kb0;  // slots [lo, hi) are open for this warp
+      while (lo < kb1) {
+        // open further slots that the tensor-core warp has released; wait when none is open
+        while (hi < kb1 && hi < lo + SA) {
+          const int s = hi & (SA - 1);
+          const uint32_t ph = ((a_empty_ph >> s) & 1u) ^ 1u;
+          if (hi == lo) {
+            if (!mbar_wait(a_empty_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
+          } else if (!mbar_test_wait(a_empty_bar(s), ph)) {
+            break;
+          }
+          a_empty_ph ^= 1u << s;
+          ++hi;
+          // clear this warp's rows of the slot: 8 rows x 128 bytes, 32 bytes per lane
+          const uint32_t z = smem_base + s * A_ATOM_BYTES + dw * (kRowsPerWarp * 128) + lane * 32;
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(z), "r"(0u) : "memory");
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(z + 16u), "r"(0u) : "memory");
+        }
+        if (!ok) break;
+        const uint32_t open_end = static_cast<uint32_t>(hi) * 64u;
+        // everything but the newest top-ups has landed; make it (and the cleared rows)
+        // visible to the warp
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncwarp();
+        Window<IT> w[kIters];
+        int base[kIters];
 #pragma unroll
         for (int i = 0; i < kIters; ++i) {
-          const int row_local = dw * kRowsPerWarp + i * 4 + grp;
-          const int row = tile * BM + row_local;
-          const bool in = row < prm.s_m;
-          rstart[i] = in ? __ldg(prm.s_row_offsets + row) : 0;
-          rend[i] = in ? __ldg(prm.s_row_offsets + row + 1) : 0;
-          cur[i] = rstart[i];
-          if (kb0 > 0)  // this part starts inside the row: first nonzero with column >= kb0 * BK
-            cur[i] = group_lower_bound<IT>(cols, rstart[i], rend[i], kb0 * BK, sl, gmask);
-          vring[i] = ring_base + row_local * (kRing * 2u);
-          cring[i] = ring_base + BM * (kRing * 2u) + row_local * (kRing * static_cast<uint32_t>(sizeof(IT)));
-          const int g0 = cur[i] >> 3;
-          ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + sl, rend[i], nnz);
-          ring_issue<IT>(vring[i], cring[i], vals, cols, g0 + 8 + sl, rend[i], nnz);
-          filled[i] = g0 + kRingGranules;
+          base[i] = cur[i] & ~7;
+          ring_read<IT>(w[i], vring[i], cring[i], base[i] + sl * 8, cur[i], rend[i], rg_mask);
+        }
+        uint32_t bound = 0xffffffffu;  // every row of this warp is done below this column
+#pragma unroll
+        for (int i = 0; i < kIters; ++i) {
+          const int nv = scatter_open<IT>(w[i], open_end, row_swz[i], slot_mask);
+          const int tot = group8_sum(nv);
+          const int avail = min(rend[i], base[i] + 64) - cur[i];  // nonzeros of the row in the window
+          const uint32_t last_col = __shfl_sync(0xffffffffu, window_index(w[i], 7), grp * 8 + 7);
+          cur[i] += tot;
+          // cut at the end of the open slots | row finished | window used up: the row's next
+          // column is above the window's last one
+          const uint32_t b = tot < avail ? open_end : (cur[i] >= rend[i] ? 0xffffffffu : last_col + 1u);
+          bound = b < bound ? b : bound;
+        }
+        // top the rings up to one ring size past the new window bases
+#pragma unroll
+        for (int i = 0; i < kIters; ++i) {
+          const int limit = (cur[i] >> 3) + rg;
+          const int g = filled[i] + sl;
+          if (g < limit) ring_issue<IT>(vring[i], cring[i], vals, cols, g, rend[i], nnz, rg_mask);
+          filled[i] = limit > filled[i] ? limit : filled[i];
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.commit_group;" ::: "memory");  // so that wait_group 1 covers the fill
-      }
-      for (int kb = kb0; kb < kb1; ++kb, ++it) {
-        const int s = it % S;
-        const uint32_t ph = (it / S) & 1u;
-        if (sparse) {
-          // the producer had the TMA engine clear this stage (after the MMAs released it)
-          if (!mbar_wait(zero_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
-          const uint32_t a_base = smem_base + s * stage_bytes;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const uint32_t kbeg = static_cast<uint32_t>(kb * BK + h * 64);
-            // everything but the newest top-up has landed; make it visible to the warp
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-            __syncwarp();
-            Window<IT> w[kIters];
-            int base[kIters], nv[kIters];
-            uint32_t row_swz[kIters];
-            bool more[kIters];
-            bool any_more = false;
-#pragma unroll
-            for (int i = 0; i < kIters; ++i) {
-              const int row_local = dw * kRowsPerWarp + i * 4 + grp;
-              row_swz[i] = (a_base + h * A_ATOM_BYTES + row_local * 128) ^
-                           (static_cast<uint32_t>(row_local & 7) << 4);
-              base[i] = cur[i] & ~7;
-              ring_read<IT>(w[i], vring[i], cring[i], base[i] + sl * 8, rstart[i], rend[i]);
-            }
-#pragma unroll
-            for (int i = 0; i < kIters; ++i) nv[i] = scatter_window<IT>(w[i], kbeg, row_swz[i]);
-#pragma unroll
-            for (int i = 0; i < kIters; ++i) {
-              cur[i] += group8_sum(nv[i], gmask);
-              more[i] = (cur[i] == base[i] + 64) && (cur[i] < rend[i]);
-              any_more |= more[i];
-            }
-            if (__any_sync(0xffffffffu, any_more)) {  // some run is longer than its window
-              asm volatile("cp.async.wait_group 0;" ::: "memory");
-              __syncwarp();
-#pragma unroll
-              for (int i = 0; i < kIters; ++i) {
-                int n2 = 0;
-                if (more[i]) {
-                  ring_read<IT>(w[i], vring[i], cring[i], base[i] + 64 + sl * 8, rstart[i], rend[i]);
-                  n2 = scatter_window<IT>(w[i], kbeg, row_swz[i]);
-                }
-                cur[i] += group8_sum(n2, gmask);
-              }
-            }
-            // top the rings up to kRing positions past the new window bases
-#pragma unroll
-            for (int i = 0; i < kIters; ++i) {
-              const int limit = (cur[i] >> 3) + kRingGranules;
-              const int g = filled[i] + sl;
-              if (g < limit) ring_issue<IT>(vring[i], cring[i], vals, cols, g, rend[i], nnz);
-              filled[i] = limit > filled[i] ? limit : filled[i];
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        } else {
-          if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 32)) { ok = false; break; }
+        {
+          const uint32_t o8 = __shfl_xor_sync(0xffffffffu, bound, 8);
+          bound = o8 < bound ? o8 : bound;
+          const uint32_t o16 = __shfl_xor_sync(0xffffffffu, bound, 16);
+          bound = o16 < bound ? o16 : bound;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full_bar(s));
+        int ready = static_cast<int>(bound >> 6);
+        ready = ready > hi ? hi : ready;
+        if (ready > lo) {
+          if (ready == kb1)  // nothing of this unit may still be landing when its last slot goes
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0)
+            for (int j = lo; j < ready; ++j) mbar_arrive(a_full_bar(j & (SA - 1)));
+          lo = ready;
+        }
       }
-      if (sparse) {  // nothing of this unit may still be landing when the rings are reused
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncwarp();
-      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncwarp();
     }
   }
 
@@ -765,13 +870,52 @@ int* status_word() {
   return p;
 }
 
+// Shared-memory budget for stages / slots / rings (227 KB per CTA minus alignment slack and
+// the mbarrier block).
+constexpr int kBarBytes = 8 * (2 * kMaxStages + 2 * kMaxASlots + 2 * kMaxBSlots + 2) + 16;
+constexpr int kDataBudget = 227 * 1024 - 1024 - kBarBytes - 64;
+
+int dense_stages(int n, int cap) {
+  const int stage_bytes = A_STAGE_BYTES + n * 256;
+  const int stages = kDataBudget / stage_bytes;
+  return stages > cap ? cap : stages;
+}
+
+// Sparse plan: as many A slots (64 columns of the 128-row tile, 16 KB) and B slots (the
+// matching 64 rows of X) as fit beside the CSR rings.
+bool sparse_plan(int n, int index_bits, int* a_slots, int* b_slots) {
+  const int ring = BM * kRingGranules * 8 * (2 + index_bits / 8);
+  static const int kPlans[4][2] = {{8, 4}, {4, 4}, {4, 2}, {2, 2}};
+  for (const auto& pl : kPlans) {
+    if (pl[0] * A_ATOM_BYTES + pl[1] * n * 128 + ring <= kDataBudget) {
+      *a_slots = pl[0];
+      *b_slots = pl[1];
+      return true;
+    }
+  }
+  return false;
+}
+
 template <int ND, typename IT>
 int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMap& tbs, Params prm,
                  int stages, int ctas_per_sm, cudaStream_t stream) {
   prm.num_stages = stages;
-  const size_t ring = ND > 0 ? static_cast<size_t>(BM) * kRing * (2 + sizeof(IT)) : 0;
-  const size_t smem = 1024 + static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256) +
-                      8 * (3 * stages + 4) + 32 + ring;
+  size_t data = static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256);
+  prm.s_a_slots = 1;
+  prm.s_b_slots = 1;
+  prm.s_ring_offset = 0;
+  if (ND > 0) {
+    if (!sparse_plan(prm.n, 8 * static_cast<int>(sizeof(IT)), &prm.s_a_slots, &prm.s_b_slots))
+      return IEX_ERR_UNSUPPORTED;
+    const size_t ring = static_cast<size_t>(BM) * kRingGranules * 8 * (2 + sizeof(IT));
+    prm.s_ring_offset = static_cast<uint32_t>(prm.s_a_slots * A_ATOM_BYTES + prm.s_b_slots * prm.n * 128);
+    const size_t sparse = prm.s_ring_offset + ring;
+    data = sparse > data ? sparse : data;
+  }
+  data = (data + 15) & ~static_cast<size_t>(15);
+  if (stages > kMaxStages || data > static_cast<size_t>(kDataBudget)) return IEX_ERR_UNSUPPORTED;
+  prm.bar_offset = static_cast<uint32_t>(data);
+  const size_t smem = 1024 + data + kBarBytes;
   auto kern = tc_units_kernel<ND, IT>;
   static size_t configured = 0;
   if (smem > configured) {
@@ -817,14 +961,6 @@ extern "C" int iex_last_device_status(int clear) {
 
 namespace {
 
-// Stages that fit beside the CSR rings in one CTA's shared memory (one CTA per SM).
-int sparse_stages(int n, int index_bits) {
-  const int ring = BM * kRing * (2 + index_bits / 8);
-  const int stage_bytes = A_STAGE_BYTES + n * 256;
-  int stages = (224 * 1024 - ring) / stage_bytes;
-  return stages > 4 ? 4 : stages;
-}
-
 int sparse_args_ok(int m, int k, int n, int nnz, const int32_t* row_offsets, const void* cols,
                    const void* values, const void* dense, const void* out, int index_bits) {
   if (m < 0 || k < 0 || n < 0 || nnz < 0) return IEX_ERR_BAD_ARG;
@@ -844,8 +980,9 @@ size_t workspace_bytes(int s_tiles, int s_parts, int d_tiles, int d_parts, int n
 
 // Clamps the part counts to the number of k-blocks and points the kernel at the workspace.
 int bind_workspace(Params& p, int s_parts, int d_parts, void* workspace, size_t bytes) {
-  const int k_blocks = (p.k + BK - 1) / BK;
-  p.s_parts = s_parts < 1 ? 1 : (s_parts > k_blocks ? k_blocks : s_parts);
+  const int k_blocks = (p.k + BK - 1) / BK;  // dense units advance 128 columns per stage
+  const int k_slots = (p.k + 63) / 64;       // sparse units 64 columns per slot
+  p.s_parts = s_parts < 1 ? 1 : (s_parts > k_slots ? k_slots : s_parts);
   p.d_parts = d_parts < 1 ? 1 : (d_parts > k_blocks ? k_blocks : d_parts);
   if (p.s_tiles == 0) p.s_parts = 1;
   if (p.d_tiles == 0) p.d_parts = 1;
@@ -885,9 +1022,7 @@ int linear_impl(int tokens, int in_features, int out_features, const void* input
   p.status = status_word();
   st = bind_workspace(p, 1, parts, workspace, bytes);
   if (st) return st;
-  const int stage_bytes = A_STAGE_BYTES + tokens * 256;
-  int stages = (220 * 1024) / stage_bytes;
-  stages = stages > 6 ? 6 : stages;
+  const int stages = dense_stages(tokens, kMaxStages);
   if (stages < 2) return IEX_ERR_UNSUPPORTED;
   return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
 }
@@ -909,8 +1044,10 @@ int fused_impl(int m_sparse, int m_dense, int k, int n, int nnz, const int32_t* 
   if (st) return st;
   if (m_dense > 0 && (!weight || !out_dense || !aligned16(weight))) return IEX_ERR_BAD_ARG;
   if (m_sparse == 0 && m_dense == 0) return IEX_OK;
-  CUtensorMap ta, tb;
-  st = make_map(&tb, x, k, n, BK);
+  CUtensorMap ta, tb, tbs;
+  st = make_map(&tb, x, k, n, BK);   // dense units: [128 k-rows x 64 cols] boxes of X
+  if (st) return st;
+  st = make_map(&tbs, x, k, n, 64);  // sparse units: [64 k-rows x 64 cols]
   if (st) return st;
   if (m_dense > 0) {
     st = make_map(&ta, weight, m_dense, k, BM);
@@ -938,11 +1075,11 @@ int fused_impl(int m_sparse, int m_dense, int k, int n, int nnz, const int32_t* 
   p.status = status_word();
   st = bind_workspace(p, sparse_parts, dense_parts, workspace, bytes);
   if (st) return st;
-  const int stages = sparse_stages(n, index_bits);
+  const int stages = dense_stages(n, 4);
   if (stages < 2) return IEX_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (index_bits == 16) return launch_units<kDecodeWarps, uint16_t>(ta, tb, tb, p, stages, 1, s);
-  return launch_units<kDecodeWarps, int>(ta, tb, tb, p, stages, 1, s);
+  if (index_bits == 16) return launch_units<kDecodeWarps, uint16_t>(ta, tb, tbs, p, stages, 1, s);
+  return launch_units<kDecodeWarps, int>(ta, tb, tbs, p, stages, 1, s);
 }
 
 }  // namespace
