@@ -4,21 +4,26 @@
 //   * fused sparse || dense both of the above in ONE launch, sharing X.
 //
 // One persistent, warp-specialised CTA design serves all three.  A CTA walks a list of
-// work units; a unit is one 128-row tile of either branch over the whole K range.  Per
-// unit the CTA runs a ring of shared-memory stages, each holding a 128x128 fp16 A tile
-// and a 128xN fp16 B tile in the 128-byte-swizzled layout tcgen05.mma reads:
+// work units; a unit is one 128-row tile of either branch over the whole K range (or one
+// part of it).  Shared memory holds, for a dense unit, a ring of stages of a 128x128 fp16 A
+// tile and a 128xN fp16 B tile; for a sparse unit, a ring of up to eight "A slots" (64
+// columns of the tile, 16 KB each), a shorter ring of B slots (the matching 64 rows of X) and
+// a ring of 128 nonzeros per row of the CSR stream -- all in the 128-byte-swizzled layout
+// tcgen05.mma reads.  The two plans overlay each other; a CTA that changes kind between two
+// units waits for the first to finish.
 //
-//   warp 0      TMA producer: B tile (activations X) for every unit, A tile (W) for dense
+//   warp 0      TMA producer: B tiles (activations X) for every unit, A tiles (W) for dense
 //               units, with cp.async.bulk.tensor + mbarrier complete_tx.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=tokens, K=16) into a
-//               TMEM accumulator and releases stages with tcgen05.commit.
+//               TMEM accumulator and releases stages / slots with tcgen05.commit.
 //   warps 2-5   epilogue: tcgen05.ld the accumulator (lane = output row), convert to
 //               fp16, store.
 //   warps 6..   CSR decoders (sparse units): stream the rows' values and column indices
-//               with 128-bit loads straight from the CSR arrays (no re-packed format, no
-//               per-tile metadata: a cursor per row advances through the ascending column
-//               indices), and scatter them into the zero-filled A stage in the swizzled
-//               operand layout, then fence.proxy.async + mbarrier arrive.
+//               with 16-byte cp.async copies straight from the CSR arrays (no re-packed
+//               format, no per-tile metadata: a cursor per row advances through the
+//               ascending column indices) and scatter every nonzero into whichever open A
+//               slot its column falls in, then fence.proxy.async + mbarrier arrive for the
+//               slots all their rows have passed.
 //
 // Dense units cost almost no instructions (TMA + MMA), sparse units are instruction-bound
 // in the decoders, and both are fed from HBM, so co-resident CTAs working on units of
@@ -290,23 +295,32 @@ __device__ __forceinline__ void ring_read(Window<IT>& w, uint32_t vring, uint32_
   }
 }
 
-// Writes the window's nonzeros whose column is below open_end into the A slots.  A slot is
-// one 64-column swizzle atom ([128 rows x 128 bytes]); the slots of consecutive 64-column
-// blocks lie 16 KB apart in a power-of-two ring, so the slot of a column is a bit field of
-// the column index: address = row part ^ (column-in-atom part) + (slot part).
+// Writing a window into the A slots.  A slot is one 64-column swizzle atom ([128 rows x 128
+// bytes]); the slots of consecutive 64-column blocks lie 16 KB apart in a power-of-two ring,
+// so the slot of a column is a bit field of the column index:
+//   address = (row part ^ column-in-atom part) + slot part.
 // row_swz = (A region + row * 128) ^ ((row & 7) << 4); XOR-ing the byte column into it
-// applies the 128-byte swizzle.  Returns how many were written.
+// applies the 128-byte swizzle.  slot_bits = (slots - 1) << 6 selects the slot field.
+__device__ __forceinline__ uint32_t slot_address(uint32_t c, uint32_t row_swz, uint32_t slot_bits) {
+  return (row_swz ^ ((c << 1) & 126u)) + ((c & slot_bits) << 8);
+}
+template <typename IT>
+__device__ __forceinline__ uint16_t window_value(const Window<IT>& w, int e) {
+  return static_cast<uint16_t>((e & 1) ? (w.v[e >> 1] >> 16) : w.v[e >> 1]);
+}
+// Writes the window's nonzeros whose column is below open_end (masked positions hold the
+// largest index and never are) and returns how many those were.
 template <typename IT>
 __device__ __forceinline__ int scatter_open(const Window<IT>& w, uint32_t open_end, uint32_t row_swz,
-                                            uint32_t slot_mask) {
+                                            uint32_t slot_bits) {
   int nvalid = 0;
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     const uint32_t c = window_index(w, e);
     if (c < open_end) {
-      const uint16_t hv = static_cast<uint16_t>((e & 1) ? (w.v[e >> 1] >> 16) : w.v[e >> 1]);
-      const uint32_t addr = (row_swz ^ ((c & 63u) << 1)) + ((c << 8) & slot_mask);
-      asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(hv) : "memory");
+      asm volatile("st.shared.u16 [%0], %1;" ::"r"(slot_address(c, row_swz, slot_bits)),
+                   "h"(window_value(w, e))
+                   : "memory");
       ++nvalid;
     }
   }
@@ -620,9 +634,10 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // and writes those whose column lies below the end of the open slots -- wherever they
     // fall among these -- so no nonzero is read twice except where a window is cut at that
     // end.  Open slots are the ones the tensor-core warp is done with (the warp then clears
-    // its own rows of the slot) and this warp has not yet released.  A warp releases slot j (arrives on its full barrier) once every one of its
-    // rows has moved past column 64 * (j + 1); the tensor-core warp consumes a slot when all
-    // decoder warps have released it and X's rows for it have landed.
+    // its own rows of the slot) and this warp has not yet released.  A warp releases slot j
+    // (arrives on its full barrier) once every one of its rows has moved past column
+    // 64 * (j + 1); the tensor-core warp consumes a slot when all decoder warps have released
+    // it and X's rows for it have landed.
     // After each round the ring is topped up to one ring size past the new cursor, so
     // global-memory latency is a round away from use.
     constexpr int kNd = ND > 0 ? ND : 1;
@@ -638,7 +653,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     const uint32_t ring_base = smem_base + prm.s_ring_offset;  // 16-byte aligned
     constexpr int rg = kRingGranules;
     constexpr uint32_t rg_mask = static_cast<uint32_t>(rg - 1);
-    const uint32_t slot_mask = static_cast<uint32_t>(SA - 1) << 14;
+    const uint32_t slot_bits = static_cast<uint32_t>(SA - 1) << 6;
     uint32_t unit_it = 0, a_empty_ph = 0;
     bool ok = true, prev_sparse = false;
     for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++unit_it) {
@@ -705,8 +720,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         uint32_t bound = 0xffffffffu;  // every row of this warp is done below this column
 #pragma unroll
         for (int i = 0; i < kIters; ++i) {
-          const int nv = scatter_open<IT>(w[i], open_end, row_swz[i], slot_mask);
-          const int tot = group8_sum(nv);
+          const int tot = group8_sum(scatter_open<IT>(w[i], open_end, row_swz[i], slot_bits));
           const int avail = min(rend[i], base[i] + 64) - cur[i];  // nonzeros of the row in the window
           const uint32_t last_col = __shfl_sync(0xffffffffu, window_index(w[i], 7), grp * 8 + 7);
           cur[i] += tot;
