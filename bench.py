@@ -578,7 +578,9 @@ def other_configs_section(dev) -> dict:
 def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dict:
     """Configuration 5: 32 ReLU-sparse FFN down projections, fp16, 256 tokens.  The activation
     CSR (256x11008, 90 % zeros) is replicated; W_down (11008x4096) is sharded by columns over
-    the ranks; each layer all-gathers the [256, 4096/G] outputs with NCCL.  The local product
+    the ranks; each layer gathers the [256, 4096/G] outputs on every rank, either with an NCCL
+    all-gather or by the linear kernel's own stores into the peers' buffers followed by a
+    barrier kernel (both are timed; the faster one is reported).  The local product
     expands the activation CSR to a dense [256, 11008] tile operand and runs the tensor-core
     linear on this rank's slab (stored [4096/G, 11008], K-major)."""
     from intrasm_engine_b200 import _lib, synthetic as syn
@@ -604,10 +606,21 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
     out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)
     dense = torch.empty((tokens, k), dtype=torch.float16, device=dev)
 
+    peer = None
+    if world > 1:
+        from intrasm_engine_b200.pytorch.distributed import PeerGather
+        peer = PeerGather(tokens, n, rank, world, dev)
+
     def layer_fn(i, gather=True):
         vals, ro, ci, _nnz = acts[i % 4]
         _lib.call("iex_csr_to_dense_f16", tokens, k, ro.data_ptr(), ci.data_ptr(), 32, vals.data_ptr(),
                   dense.data_ptr(), st)
+        if gather == "peer":
+            # the linear's own threads store the slab into every rank's result buffer; one
+            # small barrier kernel per layer orders the stores before the next use
+            peer.linear(i % 2, dense, w[i % slabs], parts, ws, st)
+            peer.barrier(st)
+            return peer.result(i % 2)
         _lib.call("iex_linear_f16_splitk", tokens, k, n_local, dense.data_ptr(), w[i % slabs].data_ptr(),
                   out_local.data_ptr(), parts, ws.data_ptr(), ws.numel(), st)
         return all_gather_columns(out_local) if (gather and world > 1) else out_local
@@ -618,7 +631,7 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
 
     # The stack is launch-bound when driven from Python (3-4 launches per layer), so each
     # variant is captured once into a CUDA graph (kernels and NCCL all-gathers) and replayed.
-    def timed(gather: bool) -> float:
+    def timed(gather) -> float:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -646,18 +659,23 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    ms = timed(True)
-    ms_nogather = timed(False) if world > 1 else ms
+    ms_nccl = timed(True)
+    ms_nogather = timed(False) if world > 1 else ms_nccl
+    ms_peer = timed("peer") if world > 1 else ms_nccl
     if dist is not None:
-        tt = torch.tensor([ms, ms_nogather], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms_nccl, ms_nogather, ms_peer], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, ms_nogather = float(tt[0]), float(tt[1])
+        ms_nccl, ms_nogather, ms_peer = float(tt[0]), float(tt[1]), float(tt[2])
+    ms = min(ms_nccl, ms_peer)
+    status = _lib.lib.iex_last_device_status(0)
     nnz = acts[0][3]
     peak, _ = measured_peak_gbs()
     by = nnz * 6 + 4 * (tokens + 1) + 4 * tokens + k * n_local * 2 + tokens * n_local * 2
     return {"workload": "cfg5: 32 x (act 256x11008 CSR@90% x W_down 11008x4096 fp16), W_down column-sharded",
             "layers": layers, "gpus": world, "split_k_parts": parts, "us_per_layer": ms / layers * 1e3,
-            "us_per_layer_without_allgather": ms_nogather / layers * 1e3,
+            "us_per_layer_peer_store_gather": ms_peer / layers * 1e3,
+            "us_per_layer_nccl_allgather": ms_nccl / layers * 1e3,
+            "us_per_layer_without_allgather": ms_nogather / layers * 1e3, "device_status": status,
             "useful_gflops": 2.0 * nnz * n / (ms / layers * 1e-3) / 1e9,
             "bytes_per_layer_per_gpu": by, "frac_hbm_per_gpu": by / (ms_nogather / layers * 1e-3) / 1e9 / peak}
 

@@ -182,6 +182,33 @@ IEX_API int iex_linear_f16_splitk_static(int tokens, int in_features, int out_fe
                                          const void* input, const void* weight, void* out,
                                          int parts, void* stream);
 
+/* Column-sharded linear whose all-gather is done by the kernel's own stores.  Rank `rank` of
+ * `world` GPUs of one box (<= 8) computes its [tokens, out_features] slab of a wider
+ * [tokens, ld_out] result -- columns [col_offset, col_offset + out_features) -- and the
+ * threads that produce it store it into EVERY rank's copy of the result: outs[r] (a host
+ * array of `world` device pointers) is rank r's [tokens, ld_out] buffer, reachable from this
+ * GPU (peer access over NVLink, e.g. CUDA IPC or symmetric memory).  This replaces the
+ * per-layer NCCL all-gather of the column-sharded FFN down projection; the reference has no
+ * multi-GPU code (layers_and_funcs/torch.py:34-36 is an empty MyLinearPartitioned).  Other
+ * arguments as iex_linear_f16_splitk.  col_offset and ld_out must be multiples of 8.
+ * The stores are plain global stores; follow the call with iex_peer_barrier() before any
+ * rank reads the gathered result. */
+IEX_API int iex_linear_f16_splitk_gather(int tokens, int in_features, int out_features,
+                                         const void* input, const void* weight, void* const* outs,
+                                         int world, int rank, long long ld_out, long long col_offset,
+                                         int parts, void* workspace, size_t workspace_bytes,
+                                         void* stream);
+
+/* Barrier among the `world` GPUs of one box, enqueued on `stream`: one small kernel that
+ * makes this GPU's earlier stores visible system-wide, publishes a new epoch in every
+ * rank's signal array and waits until every rank's epoch has arrived here.  signals[r] (host
+ * array of `world` device pointers) is rank r's array of world + 1 uint32 words, zeroed
+ * once before the first barrier and reachable from every GPU.  Every rank must enqueue the
+ * same sequence of barriers.  The wait is bounded (a fraction of a second); when it gives
+ * up, IEX_ERR_TIMEOUT is left for iex_last_device_status() and the kernel returns.  No
+ * counterpart in the reference. */
+IEX_API int iex_peer_barrier(void* const* signals, int world, int rank, void* stream);
+
 /* Dense fp16 copy of a CSR matrix: out [m, k] row-major, zeros where nothing is stored.
  * The device-side counterpart of the CSR <-> dense conversions the reference delegates to
  * xformers (intrasm_engine/pytorch/utils.py:143-153); used to hand an activation CSR to the

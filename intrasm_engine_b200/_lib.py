@@ -53,6 +53,11 @@ SIGNATURES = {
     # tokens in_features out_features input weight out parts stream
     "iex_linear_f16_splitk_static": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
     # m k row_offsets cols index_bits values out stream
+    # tokens in_features out_features input weight outs world rank ld_out col_offset parts ws ws_bytes stream
+    "iex_linear_f16_splitk_gather": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, ctypes.POINTER(c_ptr), c_int,
+                                             c_int, c_ll, c_ll, c_int, c_ptr, c_size, c_ptr]),
+    # signals world rank stream
+    "iex_peer_barrier": (c_int, [ctypes.POINTER(c_ptr), c_int, c_int, c_ptr]),
     "iex_csr_to_dense_f16": (c_int, [c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)

@@ -52,6 +52,7 @@ constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
 constexpr int kFirstDecodeWarp = 6;
 constexpr int kDecodeWarps = 16;          // CSR decoder warps of the sparse-capable instance
 constexpr uint32_t kSpinLimit = 1u << 23;  // mbarrier polls (with back-off) before a wait gives up
+constexpr int kMaxPeers = 8;              // GPUs of one box
 constexpr int kMaxStages = 6;             // dense stages (barrier slots reserved)
 constexpr int kMaxASlots = 8;             // sparse A slots of 64 columns (a power of two)
 constexpr int kMaxBSlots = 4;             // sparse B slots (X rows of one 64-column block)
@@ -62,6 +63,10 @@ struct Params {
   int d_tiles, d_m;
   __half* d_out;
   long long d_stride_m, d_stride_n;
+  // further copies of the dense output (the same slab in peer GPUs' buffers), written with
+  // plain stores over NVLink by the same threads that write d_out
+  __half* d_out_copies[kMaxPeers - 1];
+  int d_num_copies;
   int d_b_mn;  // B operand of the dense branch is MN-major ([K, N]) instead of K-major ([N, K])
   // sparse branch: out[r * n + t]
   int s_tiles, s_m, s_nnz;
@@ -606,22 +611,26 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) dst[i * BM] = __uint_as_float(r[i]);
         } else if (row < rows) {
-          if (sn == 1) {
-            uint4* dst = reinterpret_cast<uint4*>(out + row * sm + c0);
+          const int copies = sparse ? 0 : prm.d_num_copies;
+          for (int pe = 0; pe <= copies; ++pe) {
+            __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
+            if (sn == 1) {
+              uint4* dst = reinterpret_cast<uint4*>(o + row * sm + c0);
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 pk;
-              __half2* h = reinterpret_cast<__half2*>(&pk);
+              for (int v = 0; v < 4; ++v) {
+                uint4 pk;
+                __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
-              for (int i = 0; i < 4; ++i)
-                h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]),
-                                         __uint_as_float(r[v * 8 + 2 * i + 1]));
-              dst[v] = pk;
+                for (int i = 0; i < 4; ++i)
+                  h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]),
+                                           __uint_as_float(r[v * 8 + 2 * i + 1]));
+                dst[v] = pk;
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                o[row * sm + (c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
             }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              out[row * sm + (c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
           }
         }
       }
@@ -819,17 +828,62 @@ tc_reduce_kernel(const Params prm) {
     const int col = f / (BM / 4), rl = (f - col * (BM / 4)) * 4;
     const int orow = tile * BM + rl;
     const float vals4[4] = {sum.x, sum.y, sum.z, sum.w};
-    if (sm == 1 && orow + 3 < rows) {  // rows contiguous in the output: one 8-byte store
-      uint2 pk;
-      __half2* h = reinterpret_cast<__half2*>(&pk);
-      h[0] = __floats2half2_rn(sum.x, sum.y);
-      h[1] = __floats2half2_rn(sum.z, sum.w);
-      __half* dst = out + orow + col * sn;
-      if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) { *reinterpret_cast<uint2*>(dst) = pk; continue; }
-    }
+    const int copies = sparse ? 0 : prm.d_num_copies;
+    for (int pe = 0; pe <= copies; ++pe) {
+      __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
+      if (sm == 1 && orow + 3 < rows) {  // rows contiguous in the output: one 8-byte store
+        uint2 pk;
+        __half2* h = reinterpret_cast<__half2*>(&pk);
+        h[0] = __floats2half2_rn(sum.x, sum.y);
+        h[1] = __floats2half2_rn(sum.z, sum.w);
+        __half* dst = o + orow + col * sn;
+        if ((reinterpret_cast<uintptr_t>(dst) & 7u) == 0) { *reinterpret_cast<uint2*>(dst) = pk; continue; }
+      }
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (orow + j < rows) out[(orow + j) * sm + col * sn] = __float2half_rn(vals4[j]);
+      for (int j = 0; j < 4; ++j)
+        if (orow + j < rows) o[(orow + j) * sm + col * sn] = __float2half_rn(vals4[j]);
+    }
+  }
+}
+
+// Barrier among the GPUs of one box over peer memory.  sig[r] points at rank r's signal
+// array of world + 1 words in memory every rank can reach: word q of rank r's array is
+// written by rank q, the last word is rank r's own epoch counter.  One block per GPU:
+// thread q publishes this rank's new epoch in rank q's array (after a system-wide fence, so
+// that everything this GPU stored before -- the output slabs in the peers' buffers -- is
+// visible first) and then waits, for a bounded time, until rank q's epoch has arrived here.
+struct PeerSignals {
+  uint32_t* sig[kMaxPeers];
+  int world, rank;
+  int* status;
+};
+constexpr uint32_t kPeerSpinLimit = 1u << 22;  // polls of ~100 ns each
+
+__global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerSignals ps) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) {
+    uint32_t* mine = ps.sig[ps.rank] + ps.world;
+    epoch_s = *mine + 1u;
+    *mine = epoch_s;
+  }
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  const int q = threadIdx.x;
+  if (q < ps.world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ps.sig[q] + ps.rank), "r"(epoch) : "memory");
+    const uint32_t* src = ps.sig[ps.rank] + q;
+    bool arrived = false;
+    for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
+      if (static_cast<int>(v - epoch) >= 0) { arrived = true; break; }
+      __nanosleep(100);
+    }
+    if (!arrived) {
+      atomicExch(ps.status, IEX_ERR_TIMEOUT);
+      atomicExch(&g_status, IEX_ERR_TIMEOUT);
+    }
   }
 }
 
@@ -1010,7 +1064,8 @@ int bind_workspace(Params& p, int s_parts, int d_parts, void* workspace, size_t 
 }
 
 int linear_impl(int tokens, int in_features, int out_features, const void* input, const void* weight,
-                void* out, int parts, void* workspace, size_t bytes, void* stream) {
+                void* out, int parts, void* workspace, size_t bytes, void* stream,
+                long long ld_out = 0, void* const* copies = nullptr, int num_copies = 0) {
   if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
   if (tokens == 0 || out_features == 0) return IEX_OK;
   if (!input || !weight || !out) return IEX_ERR_BAD_ARG;
@@ -1028,7 +1083,9 @@ int linear_impl(int tokens, int in_features, int out_features, const void* input
   p.d_m = out_features;
   p.d_out = static_cast<__half*>(out);
   p.d_stride_m = 1;
-  p.d_stride_n = out_features;
+  p.d_stride_n = ld_out > 0 ? ld_out : out_features;
+  p.d_num_copies = num_copies;
+  for (int i = 0; i < num_copies; ++i) p.d_out_copies[i] = static_cast<__half*>(copies[i]);
   p.d_b_mn = 0;
   p.k = in_features;
   p.n = tokens;
@@ -1219,4 +1276,40 @@ extern "C" int iex_linear_f16_splitk_static(int tokens, int in_features, int out
   }
   return linear_impl(tokens, in_features, out_features, input, weight, out, used_parts, ws,
                      need > 0 ? kStaticWorkspaceBytes : 0, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Column-sharded linear with the all-gather done by the kernel's own stores
+// ---------------------------------------------------------------------------------------
+extern "C" int iex_linear_f16_splitk_gather(int tokens, int in_features, int out_features,
+                                            const void* input, const void* weight, void* const* outs,
+                                            int world, int rank, long long ld_out, long long col_offset,
+                                            int parts, void* workspace, size_t workspace_bytes,
+                                            void* stream) {
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || !outs) return IEX_ERR_BAD_ARG;
+  if (ld_out < out_features || col_offset < 0 || col_offset + out_features > ld_out) return IEX_ERR_BAD_ARG;
+  if (col_offset % 8 != 0 || ld_out % 8 != 0) return IEX_ERR_UNSUPPORTED;  // 16-byte stores
+  void* copies[kMaxPeers];
+  int n = 0;
+  for (int r = 0; r < world; ++r) {
+    if (!outs[r] || !aligned16(outs[r])) return IEX_ERR_BAD_ARG;
+    if (r != rank) copies[n++] = static_cast<__half*>(outs[r]) + col_offset;
+  }
+  return linear_impl(tokens, in_features, out_features, input, weight,
+                     static_cast<__half*>(outs[rank]) + col_offset, parts, workspace, workspace_bytes,
+                     stream, ld_out, copies, n);
+}
+
+extern "C" int iex_peer_barrier(void* const* signals, int world, int rank, void* stream) {
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || !signals) return IEX_ERR_BAD_ARG;
+  PeerSignals ps{};
+  for (int r = 0; r < world; ++r) {
+    if (!signals[r] || (reinterpret_cast<uintptr_t>(signals[r]) & 3u)) return IEX_ERR_BAD_ARG;
+    ps.sig[r] = static_cast<uint32_t*>(signals[r]);
+  }
+  ps.world = world;
+  ps.rank = rank;
+  ps.status = status_word();
+  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps);
+  return launch_status();
 }

@@ -67,3 +67,51 @@ class ColumnShardedDownProj:
     def __call__(self, values, row_indices, row_offsets, column_indices, tokens: int) -> torch.Tensor:
         out = self.local(values, row_indices, row_offsets, column_indices, tokens)
         return all_gather_columns(out, self.group) if self.world > 1 else out
+
+
+class PeerGather:
+    """Buffers and calls for the all-gather that the linear kernel does with its own stores.
+
+    Every rank owns ``slots`` result buffers ``[tokens, n]`` and a signal array in symmetric
+    memory (``torch.distributed._symmetric_memory``: the same allocation on every GPU of the
+    box, mapped into every process).  ``linear(...)`` computes this rank's column slab and
+    stores it into all ranks' copies of result buffer ``slot``; ``barrier()`` then orders
+    those stores before anybody's reads.  Alternate ``slot`` between consecutive layers: a
+    rank may start storing layer L + 1 while a peer still reads layer L.
+    """
+
+    def __init__(self, tokens: int, n: int, rank: int, world: int, device, group=None, slots: int = 2):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world, self.tokens, self.n, self.slots = rank, world, tokens, n, slots
+        assert n % world == 0 and (n // world) % 8 == 0
+        self.results = symm.empty((slots, tokens, n), dtype=torch.float16, device=device)
+        self.signals = symm.empty((world + 1,), dtype=torch.int32, device=device)
+        self.results.zero_()
+        self.signals.zero_()
+        self._h_res = symm.rendezvous(self.results, group)
+        self._h_sig = symm.rendezvous(self.signals, group)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's signal words are zero before the first barrier
+        slot_bytes = tokens * n * 2
+        self._out_ptrs = [(ctypes.c_void_p * world)(*[int(p) + s * slot_bytes for p in self._h_res.buffer_ptrs])
+                          for s in range(slots)]
+        self._sig_ptrs = (ctypes.c_void_p * world)(*[int(p) for p in self._h_sig.buffer_ptrs])
+
+    def result(self, slot: int) -> torch.Tensor:
+        return self.results[slot]
+
+    def linear(self, slot: int, input: torch.Tensor, weight_slab: torch.Tensor, parts: int,
+               workspace: torch.Tensor, stream: int) -> None:
+        """``result(slot)[:, rank * n/G : (rank + 1) * n/G] = input @ weight_slab.T`` on every rank."""
+        from .. import _lib
+        n_local = self.n // self.world
+        _lib.call("iex_linear_f16_splitk_gather", self.tokens, input.size(1), n_local, input.data_ptr(),
+                  weight_slab.data_ptr(), self._out_ptrs[slot], self.world, self.rank, self.n,
+                  self.rank * n_local, parts, workspace.data_ptr(), workspace.numel(), stream)
+
+    def barrier(self, stream: int) -> None:
+        from .. import _lib
+        _lib.call("iex_peer_barrier", self._sig_ptrs, self.world, self.rank, stream)
