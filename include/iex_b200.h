@@ -216,6 +216,23 @@ IEX_API int iex_peer_barrier(void* const* signals, int world, int rank, void* st
 IEX_API int iex_csr_to_dense_f16(int m, int k, const int32_t* row_offsets, const void* column_indices,
                                  int index_bits, const void* values, void* out, void* stream);
 
+/* Dense matrix -> CSR on the device, in two calls, for the conversions the reference
+ * delegates to xformers (_dense_to_sparse, intrasm_engine/pytorch/utils.py:143-153) and for
+ * ReLU-sparse activations, which become a new CSR every layer.  dense [m, k] row-major,
+ * fp16 (value_bits 16) or fp32 (32).  An element is stored when it is != 0, or, with
+ * relu != 0, when it is > 0 (the CSR of relu(dense)).
+ *   iex_dense_to_csr_count  writes row_offsets int32[m+1] and row_indices int32[m] (rows by
+ *                           decreasing length, equal lengths in row order).  The caller then
+ *                           reads nnz = row_offsets[m] (its own copy and synchronisation)
+ *                           and allocates values[nnz] (same type as dense) and
+ *                           column_indices[nnz] (index_bits 16 or 32).
+ *   iex_dense_to_csr_fill   writes them, columns ascending inside each row.  */
+IEX_API int iex_dense_to_csr_count(int m, int k, const void* dense, int value_bits, int relu,
+                                   int32_t* row_offsets, int32_t* row_indices, void* stream);
+IEX_API int iex_dense_to_csr_fill(int m, int k, const void* dense, int value_bits, int relu,
+                                  const int32_t* row_offsets, void* values, void* column_indices,
+                                  int index_bits, void* stream);
+
 /* Last device-side failure recorded by any kernel of this library (0 = none).
  * Synchronises the device.  clear != 0 resets the word. */
 IEX_API int iex_last_device_status(int clear);

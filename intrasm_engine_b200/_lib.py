@@ -58,6 +58,10 @@ SIGNATURES = {
                                              c_int, c_ll, c_ll, c_int, c_ptr, c_size, c_ptr]),
     # signals world rank stream
     "iex_peer_barrier": (c_int, [ctypes.POINTER(c_ptr), c_int, c_int, c_ptr]),
+    # m k dense value_bits relu row_offsets row_indices stream
+    "iex_dense_to_csr_count": (c_int, [c_int, c_int, c_ptr, c_int, c_int, c_ptr, c_ptr, c_ptr]),
+    # m k dense value_bits relu row_offsets values cols index_bits stream
+    "iex_dense_to_csr_fill": (c_int, [c_int, c_int, c_ptr, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
     "iex_csr_to_dense_f16": (c_int, [c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)

@@ -1,9 +1,118 @@
-// CSR <-> dense helpers on the device (fp16), used where an activation CSR becomes the
-// tile operand of the tensor-core linear (ReLU-sparse FFN down projection).
+// CSR <-> dense helpers on the device.
+//   * csr_to_dense (fp16): where an activation CSR becomes the tile operand of the
+//     tensor-core linear (ReLU-sparse FFN down projection).
+//   * dense_to_csr (fp16 / fp32, optional ReLU): builds row_offsets, the row visiting order
+//     (rows by decreasing nnz, ties in row order), values and ascending column indices of a
+//     dense matrix in two calls: "count" (row lengths, offsets, row order) and, once the
+//     caller has read nnz = row_offsets[m] and allocated the arrays, "fill".
 #include "common.cuh"
 
 namespace iex {
 namespace {
+
+__device__ __forceinline__ bool keeps(float v, bool relu) { return relu ? v > 0.f : v != 0.f; }
+
+// One warp per row: number of stored elements of the row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+row_count_kernel(int m, int k, const T* __restrict__ dense, int relu, int* __restrict__ row_nnz) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < m; r += warps) {
+    const T* row = dense + static_cast<size_t>(r) * k;
+    int cnt = 0;
+    for (int c0 = 0; c0 < k; c0 += 32) {
+      const int c = c0 + lane;
+      const bool on = c < k && keeps(to_float(row[c]), relu != 0);
+      cnt += __popc(__ballot_sync(0xffffffffu, on));
+    }
+    if (lane == 0) row_nnz[r] = cnt;
+  }
+}
+
+// One block: row_offsets[0..m] = exclusive prefix sum of row_nnz (chunks of 1024 rows).
+__global__ void __launch_bounds__(1024) row_scan_kernel(int m, const int* __restrict__ row_nnz,
+                                                        int* __restrict__ row_offsets) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) { carry_s = 0; row_offsets[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < m; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int v = i < m ? row_nnz[i] : 0;
+    int x = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, d);
+        if (lane >= d) w += y;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int incl = x + (warp > 0 ? warp_sums[warp - 1] : 0) + carry_s;
+    if (i < m) row_offsets[i + 1] = incl;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = incl;
+    __syncthreads();
+  }
+}
+
+// Row visiting order: position of row r = number of rows with more nonzeros, plus the rows
+// before r with as many (a stable descending sort, computed as a rank: every thread compares
+// its row with all others, staged through shared memory in chunks).
+__global__ void __launch_bounds__(256) row_rank_kernel(int m, const int* __restrict__ row_nnz,
+                                                       int* __restrict__ row_indices) {
+  __shared__ int chunk[1024];
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  const int mine = r < m ? row_nnz[r] : 0;
+  int rank = 0;
+  for (int base = 0; base < m; base += 1024) {
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) chunk[i] = base + i < m ? row_nnz[base + i] : -1;
+    __syncthreads();
+    const int lim = min(1024, m - base);
+    for (int i = 0; i < lim; ++i) {
+      const int o = chunk[i];
+      rank += (o > mine || (o == mine && base + i < r)) ? 1 : 0;
+    }
+    __syncthreads();
+  }
+  if (r < m) row_indices[rank] = r;
+}
+
+// One warp per row: stored elements and their column indices, in column order.
+template <typename T, typename IT>
+__global__ void __launch_bounds__(256)
+row_fill_kernel(int m, int k, const T* __restrict__ dense, int relu, const int* __restrict__ row_offsets,
+                T* __restrict__ values, IT* __restrict__ cols) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < m; r += warps) {
+    const T* row = dense + static_cast<size_t>(r) * k;
+    int pos = row_offsets[r];
+    for (int c0 = 0; c0 < k; c0 += 32) {
+      const int c = c0 + lane;
+      const T v = c < k ? row[c] : T(0);
+      const bool on = c < k && keeps(to_float(v), relu != 0);
+      const unsigned b = __ballot_sync(0xffffffffu, on);
+      if (on) {
+        const int p = pos + __popc(b & ((1u << lane) - 1u));
+        values[p] = v;
+        cols[p] = static_cast<IT>(c);
+      }
+      pos += __popc(b);
+    }
+  }
+}
 
 // One CTA per row: clear the dense row with 128-bit stores, then scatter the row's nonzeros.
 template <typename IT>
@@ -48,5 +157,51 @@ extern "C" int iex_csr_to_dense_f16(int m, int k, const int32_t* row_offsets, co
     csr_to_dense_f16_kernel<int><<<grid, 256, 0, s>>>(m, k, row_offsets, static_cast<const int*>(column_indices),
                                                       static_cast<const __half*>(values),
                                                       static_cast<__half*>(out));
+  return launch_status();
+}
+
+extern "C" int iex_dense_to_csr_count(int m, int k, const void* dense, int value_bits, int relu,
+                                      int32_t* row_offsets, int32_t* row_indices, void* stream) {
+  using namespace iex;
+  if (m < 0 || k < 0 || (value_bits != 16 && value_bits != 32)) return IEX_ERR_BAD_ARG;
+  if (!row_offsets || !row_indices || (m > 0 && k > 0 && !dense)) return IEX_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the row lengths go to row_offsets[1..m], are ranked from there, then scanned in place
+  int* lengths = row_offsets + 1;
+  if (m > 0) {
+    const int blocks = (m + 7) / 8 < 8 * kNumSMs ? (m + 7) / 8 : 8 * kNumSMs;
+    if (value_bits == 16)
+      row_count_kernel<__half><<<blocks, 256, 0, s>>>(m, k, static_cast<const __half*>(dense), relu, lengths);
+    else
+      row_count_kernel<float><<<blocks, 256, 0, s>>>(m, k, static_cast<const float*>(dense), relu, lengths);
+    int st = launch_status();
+    if (st) return st;
+    row_rank_kernel<<<(m + 255) / 256, 256, 0, s>>>(m, lengths, row_indices);
+    st = launch_status();
+    if (st) return st;
+  }
+  row_scan_kernel<<<1, 1024, 0, s>>>(m, lengths, row_offsets);  // in place: reads [i+1], writes [i+1]
+  return launch_status();
+}
+
+extern "C" int iex_dense_to_csr_fill(int m, int k, const void* dense, int value_bits, int relu,
+                                     const int32_t* row_offsets, void* values, void* column_indices,
+                                     int index_bits, void* stream) {
+  using namespace iex;
+  if (m < 0 || k < 0 || (value_bits != 16 && value_bits != 32) || (index_bits != 16 && index_bits != 32))
+    return IEX_ERR_BAD_ARG;
+  if (index_bits == 16 && k > 65536) return IEX_ERR_UNSUPPORTED;
+  if (m == 0 || k == 0) return IEX_OK;
+  if (!dense || !row_offsets || !values || !column_indices) return IEX_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = (m + 7) / 8 < 8 * kNumSMs ? (m + 7) / 8 : 8 * kNumSMs;
+#define IEX_FILL(T, IT)                                                                              \
+  row_fill_kernel<T, IT><<<blocks, 256, 0, s>>>(m, k, static_cast<const T*>(dense), relu, row_offsets, \
+                                                static_cast<T*>(values), static_cast<IT*>(column_indices))
+  if (value_bits == 16 && index_bits == 16) IEX_FILL(__half, uint16_t);
+  else if (value_bits == 16) IEX_FILL(__half, int);
+  else if (index_bits == 16) IEX_FILL(float, uint16_t);
+  else IEX_FILL(float, int);
+#undef IEX_FILL
   return launch_status();
 }

@@ -32,6 +32,34 @@ def dense_to_sparse(matrix: torch.Tensor, device=None, index_dtype=torch.int32):
     return values, row_indices, row_offsets, column_indices
 
 
+def dense_to_sparse_cuda(matrix: torch.Tensor, index_dtype=torch.int32, relu: bool = False):
+    """``dense_to_sparse`` for a CUDA matrix (fp16 / fp32) with this library's own kernels
+    (``iex_dense_to_csr_count`` / ``_fill``): same four tensors, same ordering rules.  With
+    ``relu`` the result is the CSR of ``relu(matrix)`` (what a ReLU-sparse FFN hands to its
+    down projection).  One host read-back (nnz) sits between the two kernels' launches."""
+    from .. import _lib
+    if matrix.dim() != 2 or not matrix.is_cuda or not matrix.is_contiguous():
+        raise RuntimeError("dense_to_sparse_cuda expects a contiguous 2-D CUDA matrix")
+    if matrix.dtype not in (torch.float16, torch.float32) or index_dtype not in (torch.int16, torch.int32):
+        raise RuntimeError("dense_to_sparse_cuda: fp16 / fp32 values, int16 / int32 indices")
+    m, k = matrix.shape
+    vbits = 16 if matrix.dtype == torch.float16 else 32
+    ibits = 16 if index_dtype == torch.int16 else 32
+    with torch.cuda.device(matrix.device):
+        st = torch.cuda.current_stream(matrix.device).cuda_stream
+        row_offsets = torch.empty(m + 1, dtype=torch.int32, device=matrix.device)
+        row_indices = torch.empty(m, dtype=torch.int32, device=matrix.device)
+        _lib.call("iex_dense_to_csr_count", m, k, matrix.data_ptr(), vbits, int(relu),
+                  row_offsets.data_ptr(), row_indices.data_ptr(), st)
+        nnz = int(row_offsets[m].item())
+        values = torch.empty(nnz, dtype=matrix.dtype, device=matrix.device)
+        column_indices = torch.empty(nnz, dtype=index_dtype, device=matrix.device)
+        if nnz > 0:
+            _lib.call("iex_dense_to_csr_fill", m, k, matrix.data_ptr(), vbits, int(relu),
+                      row_offsets.data_ptr(), values.data_ptr(), column_indices.data_ptr(), ibits, st)
+    return values, row_indices, row_offsets, column_indices
+
+
 def sparse_to_dense(values, row_offsets, column_indices, m: int, k: int) -> torch.Tensor:
     rows = torch.repeat_interleave(torch.arange(m, device=values.device),
                                    (row_offsets[1:] - row_offsets[:-1]).long())

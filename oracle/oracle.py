@@ -140,6 +140,21 @@ def linear(inp, weight) -> np.ndarray:
     return res
 
 
+def dense_to_csr(dense: np.ndarray, relu: bool = False, index_dtype=np.int32):
+    """CSR of a dense matrix (of relu(dense) with ``relu``): ``(values, row_indices,
+    row_offsets, column_indices)``; rows ordered by decreasing length (stable), columns
+    ascending -- the layout intrasm_engine/pytorch/utils.py:143-153 obtains from xformers."""
+    dense = np.asarray(dense)
+    mask = dense > 0 if relu else dense != 0
+    counts = mask.sum(axis=1)
+    row_offsets = np.zeros(dense.shape[0] + 1, dtype=np.int32)
+    row_offsets[1:] = np.cumsum(counts)
+    column_indices = np.nonzero(mask)[1].astype(index_dtype)
+    values = dense[mask]
+    row_indices = np.argsort(-counts.astype(np.int64), kind="stable").astype(np.int32)
+    return values, row_indices, row_offsets, column_indices
+
+
 def validate_csr(m, k, row_indices, row_offsets, column_indices) -> int:
     """0 when the CSR triple satisfies every launcher precondition, else a rule code."""
     lib = _load()

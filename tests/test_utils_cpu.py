@@ -85,3 +85,22 @@ def test_nnz_balanced_row_split():
     assert torch.equal(U.sparse_to_dense(sv, sro, sci, e - b, 64), d[b:e])
     empty = torch.zeros(5, dtype=torch.int32)
     assert U.nnz_balanced_row_split(empty, 2) == [(0, 0), (0, 4)] or U.nnz_balanced_row_split(empty, 2)[-1][1] == 4
+
+
+def test_oracle_dense_to_csr_agrees_with_host_helper():
+    """The numpy oracle of the dense -> CSR conversion and the torch host helper agree."""
+    import numpy as np
+    import torch
+    from intrasm_engine_b200.pytorch.utils import dense_to_sparse
+    from oracle import oracle
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((37, 53)).astype(np.float32)
+    a[rng.random(a.shape) > 0.2] = 0
+    a[5] = a[20]
+    a[9] = 0
+    v, ri, ro, ci = oracle.dense_to_csr(a)
+    tv, tri, tro, tci = dense_to_sparse(torch.as_tensor(a))
+    assert np.array_equal(v, tv.numpy()) and np.array_equal(ri, tri.numpy())
+    assert np.array_equal(ro, tro.numpy()) and np.array_equal(ci, tci.numpy())
+    rv, _, rro, rci = oracle.dense_to_csr(a, relu=True)
+    assert np.all(rv > 0) and rro[-1] == (a > 0).sum() and len(rci) == len(rv)
