@@ -145,6 +145,50 @@ def test_fused_small(oracle, ms, md, k, n):
     _status_clean()
 
 
+@pytest.mark.parametrize("ms,md,k,n,idx", [
+    (15360, 15360, 264, 64, np.int16),   # 120 + 120 units on 148 CTAs: 64 CTAs run a dense unit, then a sparse one
+    (25664, 128, 256, 64, np.int32),     # 201 sparse units: CTAs run two sparse units back to back
+    (2048, 20480, 192, 128, np.int16),   # three waves, dense before and after the sparse units
+])
+def test_fused_more_units_than_ctas(oracle, ms, md, k, n, idx):
+    """CTAs that take several units, of one kind or of both (the two kinds lay shared memory
+    out differently, so a CTA that changes kind waits for its previous unit to finish)."""
+    rng = np.random.default_rng(ms + md)
+    mask = rng.random((ms, k)) < 0.4
+    mask[0] = True
+    mask[ms // 2] = False
+    a = syn.csr_from_mask(mask, rng=rng, std=0.05, dtype=np.float16, index_dtype=idx)
+    w = (rng.standard_normal((md, k)) * 0.05).astype(np.float16)
+    x = rng.standard_normal((k, n)).astype(np.float16)
+    da = G.DevCSR(a)
+    out_s, out_d = _fused(da, G.dev(w), G.dev(x))
+    ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, ms)[0]
+    ref_d = x.astype(np.float32).T @ w.astype(np.float32).T
+    assert G.close(out_s.cpu().numpy(), ref_s, RTOL, RTOL)
+    assert G.close(out_d.cpu().numpy(), ref_d, RTOL, RTOL)
+    # same bits from the sparse launch alone and from a second fused launch
+    assert torch.equal(_spmm_tc(da, G.dev(x)), out_s)
+    again_s, again_d = _fused(da, G.dev(w), G.dev(x))
+    assert torch.equal(again_s, out_s) and torch.equal(again_d, out_d)
+    _status_clean()
+
+
+@pytest.mark.parametrize("n", [192, 256])
+@pytest.mark.parametrize("idx", [np.int16, np.int32])
+def test_spmm_tc_wide_n(oracle, n, idx):
+    """Token counts whose B slots leave room for fewer A slots (other shared-memory plans)."""
+    rng = np.random.default_rng(n)
+    m, k = 300, 1160
+    mask = rng.random((m, k)) < 0.25
+    mask[3] = True
+    a = syn.csr_from_mask(mask, rng=rng, std=0.05, dtype=np.float16, index_dtype=idx)
+    b = rng.standard_normal((k, n)).astype(np.float16)
+    got = _spmm_tc(G.DevCSR(a), G.dev(b)).cpu().numpy()
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, m)[0]
+    assert G.close(got, ref, RTOL, RTOL), G.max_violation(got, ref, RTOL, RTOL)
+    _status_clean()
+
+
 def test_fused_cfg4_full_size(oracle):
     """Benchmark configuration 4: W_up 11008x4096 CSR at 50 % times X 4096x64, fused with W_qkv 12288x4096."""
     a, w, x = syn.fused_layer_case(0)
