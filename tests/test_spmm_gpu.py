@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 import torch
 
-from intrasm_engine_b200 import synthetic as syn
+from intrasm_engine_b200 import _lib, synthetic as syn
 from . import gpu_util as G
 
 pytestmark = pytest.mark.gpu
@@ -140,16 +140,26 @@ def test_spmm_cfg1_full_size(oracle):
 
 
 @pytest.mark.parametrize("rows,cols", [(512, 512), (2048, 512), (512, 2048)])
-@pytest.mark.parametrize("sparsity", [0.5, 0.9, 0.98])
+@pytest.mark.parametrize("sparsity", [0.5, 0.7, 0.8, 0.9, 0.95, 0.98])
 @pytest.mark.parametrize("n", [128, 256])
-def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n):
-    """Benchmark configuration 3 (subset of the sweep): fp16 values, fp32 accumulate, int16 indices."""
-    a, b = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n)
-    got = G.spmm_f16(G.DevCSR(a), G.dev(b)[None])[0].cpu().numpy()
+@pytest.mark.parametrize("idx", [np.int16, np.int32])
+def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n, idx):
+    """Benchmark configuration 3, the whole sweep (36 cases x 2 index widths): fp16 values,
+    fp32 accumulate.  The CUDA-core kernel is bit-exact against the oracle and within 1e-2 of
+    the torch CPU path; the tensor-core kernel within 1e-2 of the oracle."""
+    a, b = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n, index_dtype=idx)
+    da = G.DevCSR(a)
+    got = G.spmm_f16(da, G.dev(b)[None])[0].cpu().numpy()
     ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, rows)[0]
     np.testing.assert_array_equal(got, ref.astype(np.float16))
     tref = oracle.torch_spmm(a.row_offsets, a.column_indices, a.values, b, rows)
     assert G.close(got, tref, 1e-2, 1e-2)
+    tc = torch.empty((rows, n), dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_spmm_f16_tc", rows, cols, n, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
+              16 if idx == np.int16 else 32, da.values.data_ptr(), G.dev(b).data_ptr(), tc.data_ptr(),
+              G.stream_ptr())
+    assert G.close(tc.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert _lib.lib.iex_last_device_status(1) == 0
 
 
 @pytest.mark.parametrize("m,k,n,density", [(4096, 4096, 64, 0.05), (300, 2048, 128, 0.1), (777, 6000, 24, 0.02)])
