@@ -70,6 +70,7 @@ struct Params {
   int d_b_mn;  // B operand of the dense branch is MN-major ([K, N]) instead of K-major ([N, K])
   // sparse branch: out[r * n + t]
   int s_tiles, s_m, s_nnz;
+  int s_tile_rows;  // rows of a sparse tile (a multiple of 8, <= 128; rows above it stay zero)
   __half* s_out;
   const int* s_row_offsets;
   const void* s_cols;
@@ -339,27 +340,57 @@ __device__ __forceinline__ int group8_sum(int v) {
   return v;
 }
 
-// First position p in [lo, hi) with cols[p] >= key (hi when there is none), found by the 8
-// lanes of a row group together: each step probes 8 evenly spaced positions and keeps the
-// ninth of the range that holds the answer.  All lanes of the group return the same value.
-template <typename IT>
-__device__ __forceinline__ int group_lower_bound(const IT* __restrict__ cols, int lo, int hi, int key,
-                                                 int sl, unsigned gmask) {
+// For each of a warp's kIters rows (one per group of 8 lanes): the first position p in
+// [lo, hi) with cols[p] >= key (hi when there is none).  Every step each lane probes one
+// position of its row's range -- the first step around the position a uniform spread of the
+// row's columns would put the key at (16 apart), later steps evenly over what is left -- and
+// the range shrinks to the gap between the last probe below the key and the first one not
+// below it.  The rows of all groups and iterations advance together, so a step costs one
+// global-memory round trip for the whole warp; with roughly uniform columns two or three
+// steps suffice and they touch neighbouring cache lines.  lo[] is the answer on return.
+template <typename IT, int kIters>
+__device__ __forceinline__ void rows_lower_bound(const IT* __restrict__ cols, int (&lo)[kIters],
+                                                 int (&hi)[kIters], int key, int k, int sl, unsigned gmask) {
   const int shift = __ffs(gmask) - 1;
-  while (hi - lo > 8) {
-    const int step = (hi - lo + 8) / 9;            // >= 1; the probes split [lo, hi) into <= 9 runs
-    const int pos = lo + (sl + 1) * step - 1;       // last element of run sl
-    const bool below = pos < hi && to_index(__ldg(cols + pos)) < key;
-    const unsigned b = (__ballot_sync(gmask, below) >> shift) & 0xffu;
-    const int nb = __popc(b);                       // monotone: the first nb probes are below
-    const int new_lo = lo + nb * step;
-    const int new_hi = min(hi, lo + (nb + 1) * step);
-    lo = new_lo > hi ? hi : new_lo;
-    hi = new_hi;
+  bool first = true;
+  for (int guard = 0; guard < 40; ++guard) {
+    bool open = false;
+#pragma unroll
+    for (int i = 0; i < kIters; ++i) open = open || hi[i] > lo[i];
+    if (!__any_sync(0xffffffffu, open)) break;
+    int base[kIters], stride[kIters];
+    bool below[kIters];
+#pragma unroll
+    for (int i = 0; i < kIters; ++i) {
+      const int len = hi[i] - lo[i];
+      if (first) {  // around the estimate, 16 apart
+        const int est = lo[i] + static_cast<int>(static_cast<long long>(len) * key / (k > 0 ? k : 1));
+        base[i] = est - 56;
+        stride[i] = 16;
+      } else {      // evenly: the probes split the range into nine runs
+        stride[i] = (len + 8) / 9;
+        base[i] = lo[i] + stride[i] - 1;
+      }
+      int q = base[i] + sl * stride[i];
+      q = q < lo[i] ? lo[i] : (q > hi[i] - 1 ? hi[i] - 1 : q);
+      below[i] = len > 0 && to_index(__ldg(cols + q)) < key;
+    }
+#pragma unroll
+    for (int i = 0; i < kIters; ++i) {
+      const int nb = __popc((__ballot_sync(gmask, below[i]) >> shift) & 0xffu);  // monotone: a prefix
+      if (hi[i] > lo[i]) {
+        const int l0 = lo[i], h0 = hi[i];
+        auto probe = [&](int j) {
+          const int q = base[i] + j * stride[i];
+          return q < l0 ? l0 : (q > h0 - 1 ? h0 - 1 : q);
+        };
+        if (nb > 0) lo[i] = probe(nb - 1) + 1;
+        if (nb < 8) hi[i] = probe(nb);
+        if (hi[i] < lo[i]) hi[i] = lo[i];
+      }
+    }
+    first = false;
   }
-  const bool below = lo + sl < hi && to_index(__ldg(cols + lo + sl)) < key;
-  const unsigned b = (__ballot_sync(gmask, below) >> shift) & 0xffu;
-  return lo + __popc(b);
 }
 
 // ND = number of CSR decoder warps (0: dense-only instance).
@@ -584,8 +615,9 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         *units_done = unit_it + 1u;
       }
       const int row_local = q * 32 + lane;
-      const int row = tile * BM + row_local;
-      const int rows = sparse ? prm.s_m : prm.d_m;
+      const int tile_rows = sparse ? prm.s_tile_rows : BM;
+      const int row = tile * tile_rows + row_local;
+      const bool row_stored = row_local < tile_rows && row < (sparse ? prm.s_m : prm.d_m);
       __half* out = sparse ? prm.s_out : prm.d_out;
       const long long sm = sparse ? static_cast<long long>(n) : prm.d_stride_m;
       const long long sn = sparse ? 1ll : prm.d_stride_n;
@@ -610,7 +642,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                        row_local;
 #pragma unroll
           for (int i = 0; i < 32; ++i) dst[i * BM] = __uint_as_float(r[i]);
-        } else if (row < rows) {
+        } else if (row_stored) {
           const int copies = sparse ? 0 : prm.d_num_copies;
           for (int pe = 0; pe <= copies; ++pe) {
             __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
@@ -678,13 +710,20 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #pragma unroll
       for (int i = 0; i < kIters; ++i) {
         const int row_local = dw * kRowsPerWarp + i * 4 + grp;
-        const int row = tile * BM + row_local;
-        const bool in = row < prm.s_m;
-        const int rstart = in ? __ldg(prm.s_row_offsets + row) : 0;
+        const int row = tile * prm.s_tile_rows + row_local;
+        const bool in = row_local < prm.s_tile_rows && row < prm.s_m;
+        cur[i] = in ? __ldg(prm.s_row_offsets + row) : 0;
         rend[i] = in ? __ldg(prm.s_row_offsets + row + 1) : 0;
-        cur[i] = rstart;
-        if (kb0 > 0)  // this part starts inside the row: first nonzero with column >= kb0 * 64
-          cur[i] = group_lower_bound<IT>(cols, rstart, rend[i], kb0 * 64, sl, gmask);
+      }
+      if (kb0 > 0) {  // this part starts inside the rows: first nonzero with column >= kb0 * 64
+        int hi_s[kIters];
+#pragma unroll
+        for (int i = 0; i < kIters; ++i) hi_s[i] = rend[i];
+        rows_lower_bound<IT, kIters>(cols, cur, hi_s, kb0 * 64, prm.k, sl, gmask);
+      }
+#pragma unroll
+      for (int i = 0; i < kIters; ++i) {
+        const int row_local = dw * kRowsPerWarp + i * 4 + grp;
         vring[i] = ring_base + row_local * (rg * 16u);
         cring[i] = ring_base + BM * (rg * 16u) + row_local * (rg * 8u * static_cast<uint32_t>(sizeof(IT)));
         row_swz[i] = (smem_base + row_local * 128) ^ (static_cast<uint32_t>(row_local & 7) << 4);
@@ -727,9 +766,13 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           ring_read<IT>(w[i], vring[i], cring[i], base[i] + sl * 8, cur[i], rend[i], rg_mask);
         }
         uint32_t bound = 0xffffffffu;  // every row of this warp is done below this column
+        int tots[kIters];
+#pragma unroll
+        for (int i = 0; i < kIters; ++i)
+          tots[i] = group8_sum(scatter_open<IT>(w[i], open_end, row_swz[i], slot_bits));
 #pragma unroll
         for (int i = 0; i < kIters; ++i) {
-          const int tot = group8_sum(scatter_open<IT>(w[i], open_end, row_swz[i], slot_bits));
+          const int tot = tots[i];
           const int avail = min(rend[i], base[i] + 64) - cur[i];  // nonzeros of the row in the window
           const uint32_t last_col = __shfl_sync(0xffffffffu, window_index(w[i], 7), grp * 8 + 7);
           cur[i] += tot;
@@ -826,7 +869,9 @@ tc_reduce_kernel(const Params prm) {
         if (pp + u < parts) { sum.x += t[u].x; sum.y += t[u].y; sum.z += t[u].z; sum.w += t[u].w; }
     }
     const int col = f / (BM / 4), rl = (f - col * (BM / 4)) * 4;
-    const int orow = tile * BM + rl;
+    const int tile_rows = sparse ? prm.s_tile_rows : BM;
+    if (rl >= tile_rows) continue;
+    const int orow = tile * tile_rows + rl;
     const float vals4[4] = {sum.x, sum.y, sum.z, sum.w};
     const int copies = sparse ? 0 : prm.d_num_copies;
     for (int pe = 0; pe <= copies; ++pe) {
@@ -1029,6 +1074,22 @@ extern "C" int iex_last_device_status(int clear) {
 
 namespace {
 
+// Height of a sparse tile.  A sparse unit's time depends little on how many of its 128 rows
+// are in use (each decoder warp works through its own rows at the pace of its dependent
+// instructions), so when full tiles would leave SMs without a unit, lower tiles that give
+// (nearly) every SM one -- minus the SMs the dense units need, two units apiece -- finish
+// sooner.  Split-K launches keep full tiles (the workspace size promises 128-row tiles).
+int sparse_tile_rows(int m_sparse, int d_tiles, int sparse_parts) {
+  if (m_sparse <= 0 || sparse_parts > 1) return BM;
+  const int sms = sm_count();
+  const int target = sms - (d_tiles + 1) / 2;  // CTAs left for sparse units in the first wave
+  const int full = (m_sparse + BM - 1) / BM;
+  if (target <= full) return BM;
+  int h = ((m_sparse + target - 1) / target + 7) & ~7;
+  h = h < 8 ? 8 : (h > BM ? BM : h);
+  return h;
+}
+
 int sparse_args_ok(int m, int k, int n, int nnz, const int32_t* row_offsets, const void* cols,
                    const void* values, const void* dense, const void* out, int index_bits) {
   if (m < 0 || k < 0 || n < 0 || nnz < 0) return IEX_ERR_BAD_ARG;
@@ -1133,7 +1194,8 @@ int fused_impl(int m_sparse, int m_dense, int k, int n, int nnz, const int32_t* 
   if (dense_out_tokens_major) { p.d_stride_m = 1; p.d_stride_n = m_dense; }
   else { p.d_stride_m = n; p.d_stride_n = 1; }
   p.d_b_mn = 1;
-  p.s_tiles = (m_sparse + BM - 1) / BM;
+  p.s_tile_rows = sparse_tile_rows(m_sparse, (m_dense + BM - 1) / BM, sparse_parts);
+  p.s_tiles = (m_sparse + p.s_tile_rows - 1) / p.s_tile_rows;
   p.s_m = m_sparse;
   p.s_nnz = nnz;
   p.s_out = static_cast<__half*>(out_sparse);
