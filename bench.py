@@ -187,6 +187,31 @@ def run_reference(args) -> None:
 # GPU path
 # ----------------------------------------------------------------------------------------
 
+def _bind_to_gpu_numa_node(device_index: int):
+    """Restricts this process to the CPUs of the NUMA node the GPU hangs off (read from sysfs)
+    and returns the previous affinity, or None when the node cannot be determined."""
+    try:
+        pr = torch.cuda.get_device_properties(device_index)
+        bdf = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        saved = os.sched_getaffinity(0)
+        usable = cpus & saved
+        if not usable:
+            return None
+        os.sched_setaffinity(0, usable)
+        return saved
+    except (OSError, ValueError, AttributeError):
+        return None
+
+
 def run_ours(args) -> None:
     import intrasm_engine_b200  # noqa: F401  (raises if the CUDA library is missing)
     from intrasm_engine_b200 import _lib, synthetic as syn
@@ -268,6 +293,11 @@ def run_ours(args) -> None:
 
     # ---- end to end through the public torch operators, host buffers in, host result out
     ops = torch.ops.iex_ops
+    # Pinned staging memory is allocated while this process runs on the CPUs of the GPU's own
+    # NUMA node (first touch puts the pages there), so the copies do not cross sockets; the
+    # affinity is restored afterwards.
+    saved_affinity = _bind_to_gpu_numa_node(local_rank)
+
     # Each instance's six operands are packed into ONE pinned host buffer (sub-ranges aligned
     # to 256 bytes), so an instance costs one host->device copy instead of six.
     def pack(arrays):
@@ -283,6 +313,8 @@ def run_ours(args) -> None:
 
     host = [pack((q, k, v, mask.row_indices, mask.row_offsets, mask.column_indices)) for mask, q, k, v in insts]
     host_out = [torch.empty((M, K_DIM), dtype=torch.float32).pin_memory() for _ in insts]
+    if saved_affinity is not None:
+        os.sched_setaffinity(0, saved_affinity)
     h2d = sum(sum(nb for _o, nb, _d, _s in layout) for _buf, layout in host)
     d2h = sum(t.numel() * t.element_size() for t in host_out)
 

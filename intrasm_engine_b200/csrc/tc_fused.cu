@@ -36,7 +36,6 @@
 // frees its TMEM and returns.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -83,6 +82,7 @@ struct Params {
   // s_b_slots (2 or 4) B slots after them, the CSR rings at s_ring_offset; mbarriers at
   // bar_offset (past the larger of the dense and the sparse plan, which overlay each other)
   int s_a_slots, s_b_slots;
+  int s_ring_rows;      // rows the rings are laid out for (>= s_tile_rows)
   uint32_t s_ring_offset, bar_offset;
   // split-K: every tile's K range is cut into `parts` equal runs of k-blocks, one unit
   // each.  With parts > 1 a unit writes its fp32 partial tile to `partials`
@@ -725,7 +725,8 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       for (int i = 0; i < kIters; ++i) {
         const int row_local = dw * kRowsPerWarp + i * 4 + grp;
         vring[i] = ring_base + row_local * (rg * 16u);
-        cring[i] = ring_base + BM * (rg * 16u) + row_local * (rg * 8u * static_cast<uint32_t>(sizeof(IT)));
+        cring[i] = ring_base + prm.s_ring_rows * (rg * 16u) +
+                   row_local * (rg * 8u * static_cast<uint32_t>(sizeof(IT)));
         row_swz[i] = (smem_base + row_local * 128) ^ (static_cast<uint32_t>(row_local & 7) << 4);
         const int g0 = cur[i] >> 3;
         for (int j = 0; j < rg; j += 8)
@@ -748,9 +749,13 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           a_empty_ph ^= 1u << s;
           ++hi;
           // clear this warp's rows of the slot: 8 rows x 128 bytes, 32 bytes per lane
-          const uint32_t z = smem_base + s * A_ATOM_BYTES + dw * (kRowsPerWarp * 128) + lane * 32;
-          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(z), "r"(0u) : "memory");
-          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(z + 16u), "r"(0u) : "memory");
+          // (16 bytes per lane and 4 rows)
+          const uint32_t slot_addr = smem_base + s * A_ATOM_BYTES;
+#pragma unroll
+          for (int q4 = 0; q4 < kRowsPerWarp / 4; ++q4)
+            asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(
+                             slot_addr + (dw * kRowsPerWarp + q4 * 4) * 128 + lane * 16), "r"(0u)
+                         : "memory");
         }
         if (!ok) break;
         const uint32_t open_end = static_cast<uint32_t>(hi) * 64u;
@@ -995,14 +1000,16 @@ int dense_stages(int n, int cap) {
 }
 
 // Sparse plan: as many A slots (64 columns of the 128-row tile, 16 KB) and B slots (the
-// matching 64 rows of X) as fit beside the CSR rings.
-bool sparse_plan(int n, int index_bits, int* a_slots, int* b_slots) {
-  const int ring = BM * kRingGranules * 8 * (2 + index_bits / 8);
-  static const int kPlans[4][2] = {{8, 4}, {4, 4}, {4, 2}, {2, 2}};
+// matching 64 rows of X) as fit beside the CSR rings; `rows` = rows of a tile that are in use
+// (the rings are laid out for those only).  More A slots matter most; two B slots do as
+// well as four (measured).
+struct SparsePlan { int a_slots, b_slots; };
+bool sparse_plan(int n, int index_bits, int rows, SparsePlan* plan) {
+  static const SparsePlan kPlans[] = {{8, 4}, {8, 2}, {4, 4}, {4, 2}, {2, 2}};
+  const int ring = rows * kRingGranules * 8 * (2 + index_bits / 8);
   for (const auto& pl : kPlans) {
-    if (pl[0] * A_ATOM_BYTES + pl[1] * n * 128 + ring <= kDataBudget) {
-      *a_slots = pl[0];
-      *b_slots = pl[1];
+    if (pl.a_slots * A_ATOM_BYTES + pl.b_slots * n * 128 + ring <= kDataBudget) {
+      *plan = pl;
       return true;
     }
   }
@@ -1016,11 +1023,15 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
   size_t data = static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256);
   prm.s_a_slots = 1;
   prm.s_b_slots = 1;
+  prm.s_ring_rows = BM;
   prm.s_ring_offset = 0;
   if (ND > 0) {
-    if (!sparse_plan(prm.n, 8 * static_cast<int>(sizeof(IT)), &prm.s_a_slots, &prm.s_b_slots))
-      return IEX_ERR_UNSUPPORTED;
-    const size_t ring = static_cast<size_t>(BM) * kRingGranules * 8 * (2 + sizeof(IT));
+    SparsePlan plan{};
+    prm.s_ring_rows = (prm.s_tile_rows + 7) & ~7;
+    if (!sparse_plan(prm.n, 8 * static_cast<int>(sizeof(IT)), prm.s_ring_rows, &plan)) return IEX_ERR_UNSUPPORTED;
+    prm.s_a_slots = plan.a_slots;
+    prm.s_b_slots = plan.b_slots;
+    const size_t ring = static_cast<size_t>(prm.s_ring_rows) * kRingGranules * 8 * (2 + sizeof(IT));
     prm.s_ring_offset = static_cast<uint32_t>(prm.s_a_slots * A_ATOM_BYTES + prm.s_b_slots * prm.n * 128);
     const size_t sparse = prm.s_ring_offset + ring;
     data = sparse > data ? sparse : data;
