@@ -705,6 +705,34 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       // the rings overlay the stages of a dense unit before this one
       if (unit_it > 0 && !prev_sparse && !wait_units_done(unit_it)) { ok = false; break; }
       prev_sparse = true;
+      if (dw * kRowsPerWarp >= prm.s_tile_rows) {
+        // None of this warp's rows belongs to the (lower than 128 rows) tile.  Its part of the
+        // protocol: keep its rows of every slot zero -- cleared once per unit, nobody writes
+        // them afterwards -- and release each slot as soon as the tensor-core warp has let go
+        // of the slot's previous contents.
+        bool cleared = false;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const int s = kb & (SA - 1);
+          if (!mbar_wait(a_empty_bar(s), ((a_empty_ph >> s) & 1u) ^ 1u, abort_flag, prm.status, 128)) {
+            ok = false;
+            break;
+          }
+          a_empty_ph ^= 1u << s;
+          if (!cleared) {
+            if (kb - kb0 + 1 >= SA || kb + 1 == kb1) cleared = true;
+#pragma unroll
+            for (int q4 = 0; q4 < kRowsPerWarp / 4; ++q4)
+              asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(
+                               smem_base + s * A_ATOM_BYTES + (dw * kRowsPerWarp + q4 * 4) * 128 + lane * 16),
+                           "r"(0u)
+                           : "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(a_full_bar(s));
+        }
+        continue;
+      }
       int cur[kIters], rend[kIters], filled[kIters];
       uint32_t vring[kIters], cring[kIters], row_swz[kIters];
 #pragma unroll
