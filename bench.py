@@ -132,19 +132,29 @@ def flops_of(inst) -> int:
 # CPU path (reference arm and cpu_baseline)
 # ----------------------------------------------------------------------------------------
 
-def cpu_chain_seconds(inst, reps: int, warmup: int = 1):
-    """Median seconds of sampled_addmm + sparse.mm for one instance on all host threads."""
+def cpu_prepare(inst):
+    """Host tensors of one instance for the CPU path (built once, outside any timed region)."""
     from oracle import oracle as orc
     mask, q, k, v = inst
     q_t, k_t, v_t = (torch.as_tensor(x) for x in (q, k, v))
     zero = orc.torch_csr(mask.row_offsets, mask.column_indices,
                          np.zeros(mask.nnz, np.float32), M, N_COLS)
-    kt = k_t.t().contiguous()
+    return zero, q_t, k_t.t().contiguous(), v_t
+
+
+def cpu_chain_once(prepared) -> None:
+    zero, q_t, kt, v_t = prepared
+    scores = torch.sparse.sampled_addmm(zero, q_t, kt, beta=0.0)
+    torch.sparse.mm(scores, v_t)
+
+
+def cpu_chain_seconds(inst, reps: int, warmup: int = 1):
+    """Median seconds of sampled_addmm + sparse.mm for one instance on all host threads."""
+    prepared = cpu_prepare(inst)
     times = []
     for it in range(warmup + reps):
         t0 = time.perf_counter()
-        scores = torch.sparse.sampled_addmm(zero, q_t, kt, beta=0.0)
-        torch.sparse.mm(scores, v_t)
+        cpu_chain_once(prepared)
         if it >= warmup:
             times.append(time.perf_counter() - t0)
     return statistics.median(times), times
@@ -161,13 +171,14 @@ def run_reference(args) -> None:
     sample = 2
     insts = make_instances(0, sample)
     fl = sum(flops_of(i) for i in insts)
+    prepared = [cpu_prepare(inst) for inst in insts]
     for _ in range(max(args.warmup, 1)):
-        for inst in insts:
-            cpu_chain_seconds(inst, 1, 0)
+        for pr in prepared:
+            cpu_chain_once(pr)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        for inst in insts:
-            cpu_chain_seconds(inst, 1, 0)
+        for pr in prepared:
+            cpu_chain_once(pr)
     dt = time.perf_counter() - t0
     value = fl * args.steps / dt / 1e9
     line = {
