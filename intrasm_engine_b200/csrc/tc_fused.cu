@@ -196,6 +196,15 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
 
+// Descriptor of an operand `bytes` further on in shared memory: only the 14-bit address field
+// (bits 0-13, in units of 16 bytes) changes, and it cannot carry out of the field because all
+// of shared memory lies below 256 KB.  One 32-bit add per tensor-core instruction instead of
+// rebuilding the descriptor: the thread that issues them is a serial bottleneck of a unit.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
+  return (desc & 0xFFFFFFFF00000000ull) | lo;
+}
+
 // Position u of the work list -> (is_sparse, tile, part).  With S = s_tiles * s_parts sparse
 // units and D = d_tiles * d_parts dense units the list is
 //   dense[0, e)  ++  sparse[0, S)  ++  dense[e, D)      with e = clamp(D + S - grid, 0, D),
@@ -564,12 +573,12 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             tcgen05_fence_after();
             const uint32_t a_base = smem_base + sa * A_ATOM_BYTES;
             const uint32_t b_base = s_b_region + sb * s_b_slot_bytes;
+            const uint64_t adesc0 = smem_desc(a_base, 16, 1024);
+            const uint64_t bdesc0 = smem_desc(b_base, 64 * 128, 1024);
 #pragma unroll
-            for (int ks = 0; ks < 64 / UMMA_K; ++ks) {
-              const uint64_t adesc = smem_desc(a_base + ks * 32, 16, 1024);
-              const uint64_t bdesc = smem_desc(b_base + ks * (UMMA_K * 128), 64 * 128, 1024);
-              umma_f16(tmem_base, adesc, bdesc, idesc_mn, (kb != kb0 || ks != 0) ? 1u : 0u);
-            }
+            for (int ks = 0; ks < 64 / UMMA_K; ++ks)
+              umma_f16(tmem_base, desc_advance(adesc0, ks * 32), desc_advance(bdesc0, ks * (UMMA_K * 128)),
+                       idesc_mn, (kb != kb0 || ks != 0) ? 1u : 0u);
             umma_commit(a_empty_bar(sa));
             umma_commit(b_empty_bar(sb));
           }
@@ -584,14 +593,21 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             tcgen05_fence_after();
             const uint32_t a_base = smem_base + s * stage_bytes;
             const uint32_t b_base = a_base + A_STAGE_BYTES;
+            const uint64_t adesc0 = smem_desc(a_base, 16, 1024);
+            if (b_mn) {
+              const uint64_t bdesc0 = smem_desc(b_base, BK * 128, 1024);
 #pragma unroll
-            for (int ks = 0; ks < BK / UMMA_K; ++ks) {
-              const uint64_t adesc =
-                  smem_desc(a_base + (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32, 16, 1024);
-              const uint64_t bdesc =
-                  b_mn ? smem_desc(b_base + ks * (UMMA_K * 128), BK * 128, 1024)
-                       : smem_desc(b_base + (ks >> 2) * (n * 128) + (ks & 3) * 32, 16, 1024);
-              umma_f16(tmem_base, adesc, bdesc, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
+              for (int ks = 0; ks < BK / UMMA_K; ++ks)
+                umma_f16(tmem_base, desc_advance(adesc0, (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32),
+                         desc_advance(bdesc0, ks * (UMMA_K * 128)), idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
+            } else {
+              const uint64_t bdesc0 = smem_desc(b_base, 16, 1024);
+              const uint32_t b_atom = static_cast<uint32_t>(n) * 128u;  // second 64-wide K atom of B
+#pragma unroll
+              for (int ks = 0; ks < BK / UMMA_K; ++ks)
+                umma_f16(tmem_base, desc_advance(adesc0, (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32),
+                         desc_advance(bdesc0, (ks >> 2) * b_atom + (ks & 3) * 32), idesc,
+                         (kb != kb0 || ks != 0) ? 1u : 0u);
             }
             umma_commit(empty_bar(s));
           }
