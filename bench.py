@@ -613,32 +613,46 @@ def other_configs_section(dev) -> dict:
     by = syn.spmm_bytes(1024, 1024, 256, a.nnz, 4, 4)
     out["cfg1_spmm_fp32"] = {"us_per_launch_rotating": us, "gflops": syn.spmm_flops(a.nnz, 256) / us / 1e3,
                              "frac_hbm": by / us / 1e3 / peak, "bytes": by}
-    # ---- config 3: three points of the fp16 sweep (int16 indices)
+    # ---- config 3: the whole fp16 sweep (int16 indices), both kernels, and what the cost model
+    # of intrasm_engine_b200/pytorch/tuning.py would have picked
+    from intrasm_engine_b200.pytorch import tuning
     sweep = {}
-    for rows, cols, sparsity, n in ((512, 512, 0.9, 256), (2048, 512, 0.7, 128), (512, 2048, 0.95, 128)):
-        a3, b3 = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n)
-        copies3 = 48
-        c3s = [(up(a3.row_indices), up(a3.values).clone(), up(a3.row_offsets), up(a3.column_indices),
-                up(b3).clone(), torch.empty((rows, n), dtype=torch.float16, device=dev)) for _ in range(copies3)]
+    hits, regret = 0, []
+    for rows, cols in ((512, 512), (2048, 512), (512, 2048)):
+        for sparsity in (0.5, 0.7, 0.8, 0.9, 0.95, 0.98):
+            for n in (128, 256):
+                a3, b3 = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n)
+                per_copy = syn.spmm_bytes(rows, cols, n, a3.nnz, 2, 2)
+                copies3 = max(8, min(96, int(160e6 // per_copy)))  # rotate through more than L2
+                c3s = [(up(a3.row_indices), up(a3.values).clone(), up(a3.row_offsets), up(a3.column_indices),
+                        up(b3).clone(), torch.empty((rows, n), dtype=torch.float16, device=dev))
+                       for _ in range(copies3)]
 
-        def simt(i):
-            ri, va, ro, ci, bb, o = c3s[i % copies3]
-            _lib.call("iex_spmm_f16_i16", rows, cols, n, a3.nnz, ri.data_ptr(), va.data_ptr(), ro.data_ptr(),
-                      ci.data_ptr(), bb.data_ptr(), None, o.data_ptr(), 1, st)
+                def simt(i):
+                    ri, va, ro, ci, bb, o = c3s[i % copies3]
+                    _lib.call("iex_spmm_f16_i16", rows, cols, n, a3.nnz, ri.data_ptr(), va.data_ptr(),
+                              ro.data_ptr(), ci.data_ptr(), bb.data_ptr(), None, o.data_ptr(), 1, st)
 
-        def tc(i):
-            ri, va, ro, ci, bb, o = c3s[i % copies3]
-            _lib.call("iex_spmm_f16_tc", rows, cols, n, a3.nnz, ro.data_ptr(), ci.data_ptr(), 16, va.data_ptr(),
-                      bb.data_ptr(), o.data_ptr(), st)
+                def tc(i):
+                    ri, va, ro, ci, bb, o = c3s[i % copies3]
+                    _lib.call("iex_spmm_f16_tc", rows, cols, n, a3.nnz, ro.data_ptr(), ci.data_ptr(), 16,
+                              va.data_ptr(), bb.data_ptr(), o.data_ptr(), st)
 
-        by3 = syn.spmm_bytes(rows, cols, n, a3.nnz, 2, 2)
-        entry = {"nnz": a3.nnz, "bytes": by3, "cuda_core_us": _time_us(simt, iters=96, warmup=48)}
-        if n <= 128:
-            entry["tensor_core_us"] = _time_us(tc, iters=96, warmup=48)
-        best = min(v for k2, v in entry.items() if k2.endswith("_us"))
-        entry["gflops_best"] = syn.spmm_flops(a3.nnz, n) / best / 1e3
-        entry["frac_hbm_best"] = by3 / best / 1e3 / peak
-        sweep[f"{rows}x{cols}_s{sparsity}_n{n}"] = entry
+                t_simt = _time_us(simt, iters=96, warmup=48)
+                t_tc = _time_us(tc, iters=96, warmup=48)
+                pick = tuning.choose_spmm_kernel(rows, cols, n, a3.nnz)
+                t_pick = t_tc if pick == "tensor_core" else t_simt
+                best = min(t_simt, t_tc)
+                hits += int(t_pick <= best * 1.001)
+                regret.append(t_pick / best)
+                sweep[f"{rows}x{cols}_s{sparsity}_n{n}"] = {
+                    "nnz": a3.nnz, "cuda_core_us": round(t_simt, 2), "tensor_core_us": round(t_tc, 2),
+                    "model_picks": pick, "gflops_best": round(syn.spmm_flops(a3.nnz, n) / best / 1e3, 1),
+                    "frac_hbm_best": round(per_copy / best / 1e3 / peak, 4)}
+                del c3s
+    sweep["summary"] = {"cases": len(regret), "model_picked_the_faster_kernel": hits,
+                        "mean_time_vs_best": round(sum(regret) / len(regret), 3),
+                        "worst_time_vs_best": round(max(regret), 3)}
     out["cfg3_spmm_fp16_sweep"] = sweep
     return out
 

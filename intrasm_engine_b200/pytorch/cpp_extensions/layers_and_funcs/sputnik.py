@@ -5,13 +5,15 @@ Same inputs as intrasm_engine/pytorch/cpp_extensions/layers_and_funcs/sputnik.py
 dense ``[k, n]`` operand, and the same derivative scheme (:77-149):
     d values = SDDMM(grad, b) sampled at A's pattern,   d b = A^T @ grad.
 fp32 runs the CUDA-core kernels (bit-reproducible); fp16 runs the CUDA-core fp16 kernel or,
-with ``use_tensor_cores=True`` in the forward kwargs, the tcgen05 kernel.
+with ``use_tensor_cores=True`` in the forward kwargs, the tcgen05 kernel;
+``use_tensor_cores="auto"`` lets the cost model of ``pytorch/tuning.py`` choose.
 """
 from __future__ import annotations
 
 import torch
 
 from .... import ops  # noqa: F401  (registers torch.ops.iex_ops)
+from ...tuning import choose_spmm_kernel
 from ...utils import transpose_with_info
 from .utils import MyAutogradFunc, captured
 
@@ -20,6 +22,9 @@ def _spmm(b2d, row_indices, values, row_offsets, column_indices, m, use_tc=False
     if values.dtype == torch.float32:
         return torch.ops.iex_ops.spmm_sputnik_reuse_weight(b2d.unsqueeze(0), row_indices, values,
                                                            row_offsets, column_indices, m)[0]
+    if use_tc == "auto":  # cost model fitted to measurements (pytorch/tuning.py)
+        use_tc = choose_spmm_kernel(m, b2d.size(0), b2d.size(1), values.numel(), 16,
+                                    16 if column_indices.dtype == torch.int16 else 32) == "tensor_core"
     if use_tc:
         return torch.ops.iex_ops.spmm_tc_half(b2d, row_offsets, values, column_indices, m)
     return torch.ops.iex_ops.spmm_sputnik_reuse_weight_half(b2d.unsqueeze(0), row_indices, values,
