@@ -68,6 +68,21 @@ def test_myspmm_fp16_and_partitioned(oracle):
     assert torch.allclose(out_tc.float(), out.float(), rtol=2e-3, atol=2e-3 * float(out.abs().max()))
     (part,), _, _ = MySpMMPartitioned._forward(bd, da.values, da.row_offsets, da.column_indices, 256, 3)
     assert torch.equal(part, out)
+    # "auto": the cost model picks the tensor-core kernel for this case (30 % dense) ...
+    from intrasm_engine_b200.pytorch import tuning
+    assert tuning.choose_spmm_kernel(256, 512, 128, a.nnz) == "tensor_core"
+    out_auto = MySpMM.run(bd, da.row_indices, da.values, da.row_offsets, da.column_indices, 256, info,
+                          fwd_kwargs_1=default_fwd_kwargs(use_tensor_cores="auto"))
+    assert torch.equal(out_auto, out_tc)
+    # ... and the CUDA-core kernel for a 98 % sparse one
+    a2, b2 = syn.pruned_sweep_case(4, 256, 512, 0.98, 128)
+    d2 = G.DevCSR(a2)
+    assert tuning.choose_spmm_kernel(256, 512, 128, a2.nnz) == "cuda_core"
+    info2 = U.get_transpose_info(256, 512, d2.row_indices, d2.row_offsets, d2.column_indices)
+    out2 = MySpMM.run(G.dev(b2), d2.row_indices, d2.values, d2.row_offsets, d2.column_indices, 256, info2,
+                      fwd_kwargs_1=default_fwd_kwargs(use_tensor_cores="auto"))
+    ref2 = oracle.spmm(a2.row_indices, a2.values, a2.row_offsets, a2.column_indices, b2, 256)[0].astype(np.float16)
+    np.testing.assert_array_equal(out2.cpu().numpy(), ref2)
 
 
 def test_mylinear_forward_backward():
