@@ -60,7 +60,11 @@ def test_linear_golden(oracle, golden_dir):
 
 @pytest.mark.parametrize("tokens,cin,cout", [(16, 8, 8), (16, 64, 128), (64, 128, 128), (64, 256, 384),
                                              (32, 520, 200), (128, 1024, 1000), (256, 328, 640),
-                                             (48, 4096, 256), (64, 4096, 12288)])
+                                             (48, 4096, 256), (64, 4096, 12288),
+                                             # from 128 tokens on a unit holds two 128-row tiles that
+                                             # share the X stage (even, odd and single tile counts)
+                                             (128, 512, 512), (192, 776, 384), (256, 2048, 1000),
+                                             (256, 11008, 640), (256, 64, 128), (144, 1024, 300)])
 def test_linear_shapes(tokens, cin, cout):
     rng = np.random.default_rng(tokens + cin + cout)
     x = rng.standard_normal((tokens, cin)).astype(np.float16)
@@ -69,6 +73,22 @@ def test_linear_shapes(tokens, cin, cout):
     ref = x.astype(np.float32) @ w.astype(np.float32).T
     assert G.close(got, ref, RTOL, RTOL), G.max_violation(got, ref, RTOL, RTOL)
     assert G.max_violation(got, ref, 1e-3, 1e-3) < 1.0  # fp16 rounding only
+    _status_clean()
+
+
+@pytest.mark.parametrize("tokens", [16, 48, 144])
+def test_linear_writes_nothing_past_the_output(tokens):
+    """Token counts that are not a multiple of the 32 accumulator columns read at a time: the
+    rows after the output (here a guard region of the same buffer) stay untouched."""
+    rng = np.random.default_rng(tokens)
+    cin, cout = 256, 384
+    x = G.dev(rng.standard_normal((tokens, cin)).astype(np.float16))
+    w = G.dev((rng.standard_normal((cout, cin)) * 0.05).astype(np.float16))
+    buf = torch.full((tokens + 32, cout), 7.0, dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_linear_f16", tokens, cin, cout, x.data_ptr(), w.data_ptr(), buf.data_ptr(), G.stream_ptr())
+    ref = x.float() @ w.float().t()
+    assert torch.allclose(buf[:tokens].float(), ref, rtol=1e-2, atol=1e-2)
+    assert bool((buf[tokens:] == 7.0).all())
     _status_clean()
 
 
@@ -237,7 +257,8 @@ def _workspace(nbytes):
 
 
 @pytest.mark.parametrize("tokens,cin,cout,parts", [(64, 4096, 2048, 4), (32, 1024, 1000, 3), (256, 2048, 512, 8),
-                                                   (64, 256, 128, 16), (128, 640, 384, 2)])
+                                                   (64, 256, 128, 16), (128, 640, 384, 2),
+                                                   (256, 11008, 1024, 16), (192, 1000, 640, 5)])
 def test_linear_splitk(tokens, cin, cout, parts):
     rng = np.random.default_rng(tokens + cin + cout)
     x = G.dev(rng.standard_normal((tokens, cin)).astype(np.float16))
