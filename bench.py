@@ -682,8 +682,9 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
     # With few 128-row tiles per rank a tile-per-CTA schedule leaves most SMs idle and every
     # CTA is bound by its own TMA pipeline (~110 GB/s); split-K spreads a tile's K range over
     # ~128 / units CTAs.
-    groups = (tiles + 1) // 2 if tokens >= 128 else tiles  # units: pairs of tiles from 128 tokens on
-    parts = max(1, min(32, 128 // groups))
+    paired = os.environ.get("IEX_TC_PAIR") == "1" and tokens >= 128
+    groups = (tiles + 1) // 2 if paired else tiles  # units: pairs of tiles in paired mode
+    parts = max(1, min(32 if paired else 16, 128 // groups))
     need = _lib.lib.iex_tc_workspace_bytes(0, 1, n_local, parts, tokens)
     ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)

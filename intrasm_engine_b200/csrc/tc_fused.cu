@@ -36,6 +36,7 @@
 // frees its TMEM and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -1228,6 +1229,14 @@ int bind_workspace(Params& p, int s_parts, int d_parts, void* workspace, size_t 
   return IEX_OK;
 }
 
+bool pair_mode_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("IEX_TC_PAIR");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
 int linear_impl(int tokens, int in_features, int out_features, const void* input, const void* weight,
                 void* out, int parts, void* workspace, size_t bytes, void* stream,
                 long long ld_out = 0, void* const* copies = nullptr, int num_copies = 0) {
@@ -1256,7 +1265,7 @@ int linear_impl(int tokens, int in_features, int out_features, const void* input
   p.n = tokens;
   // From 128 tokens on the X tile of a stage is as large as the weight tile: two weight
   // tiles then share it (two accumulators of `tokens` TMEM columns each).
-  p.d_pair = (tokens >= 128 && 2 * tokens <= 512 && p.d_tiles >= 2) ? 1 : 0;
+  p.d_pair = (pair_mode_enabled() && tokens >= 128 && 2 * tokens <= 512 && p.d_tiles >= 2) ? 1 : 0;
   p.tmem_cols = tmem_cols_for(p.d_pair ? 2 * tokens : tokens);
   p.status = status_word();
   st = bind_workspace(p, 1, parts, workspace, bytes);
