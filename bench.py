@@ -681,10 +681,8 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
     tiles = (n_local + 127) // 128
     # With few 128-row tiles per rank a tile-per-CTA schedule leaves most SMs idle and every
     # CTA is bound by its own TMA pipeline (~110 GB/s); split-K spreads a tile's K range over
-    # ~128 / units CTAs.
-    paired = os.environ.get("IEX_TC_PAIR") == "1" and tokens >= 128
-    groups = (tiles + 1) // 2 if paired else tiles  # units: pairs of tiles in paired mode
-    parts = max(1, min(32 if paired else 16, 128 // groups))
+    # ~128 / tiles CTAs (measured optimum: 32 tiles -> 4 parts, 16 -> 8, <= 8 -> 16).
+    parts = max(1, min(16, 128 // tiles))
     need = _lib.lib.iex_tc_workspace_bytes(0, 1, n_local, parts, tokens)
     ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
     out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)

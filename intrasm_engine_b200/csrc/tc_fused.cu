@@ -36,7 +36,6 @@
 // frees its TMEM and returns.
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -68,10 +67,6 @@ struct Params {
   __half* d_out_copies[kMaxPeers - 1];
   int d_num_copies;
   int d_b_mn;  // B operand of the dense branch is MN-major ([K, N]) instead of K-major ([N, K])
-  // d_pair != 0: a dense unit covers TWO neighbouring 128-row tiles (two TMEM accumulators)
-  // that share every B stage, in stages of 64 columns.  Pays when the B tile is as large as
-  // the A tile (tokens >= 128): half as many bytes of X per weight byte through the SM's TMA.
-  int d_pair;
   // sparse branch: out[r * n + t]
   int s_tiles, s_m, s_nnz;
   int s_tile_rows;  // rows of a sparse tile (a multiple of 8, <= 128; rows above it stay zero)
@@ -219,13 +214,10 @@ __device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) 
 // so they run at the same time and reach the reduction together.
 struct Unit {
   bool sparse;
-  int tile, part, parts;  // tile: index of the 128-row tile, or of the pair of tiles (d_pair)
+  int tile, part, parts;
 };
-__host__ __device__ __forceinline__ int dense_groups(const Params& prm) {
-  return prm.d_pair ? (prm.d_tiles + 1) / 2 : prm.d_tiles;
-}
 __device__ __forceinline__ Unit unit_of(int u, const Params& prm, int grid) {
-  const int S = prm.s_tiles * prm.s_parts, D = dense_groups(prm) * prm.d_parts;
+  const int S = prm.s_tiles * prm.s_parts, D = prm.d_tiles * prm.d_parts;
   int e = D + S - grid;
   e = e < 0 ? 0 : (e > D ? D : e);
   Unit un;
@@ -422,7 +414,6 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const uint32_t b_stage_bytes = static_cast<uint32_t>(n) * 256u;
   const uint32_t stage_bytes = A_STAGE_BYTES + b_stage_bytes;
   const int S = prm.num_stages;
-  const uint32_t pair_stage_bytes = 2u * A_ATOM_BYTES + static_cast<uint32_t>(n) * 128u;  // d_pair
   // sparse units: SA A slots of 64 columns, then SB B slots (X rows of a 64-column block),
   // then the CSR rings
   const int SA = prm.s_a_slots, SB = prm.s_b_slots;
@@ -453,7 +444,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_units = dense_groups(prm) * prm.d_parts + prm.s_tiles * prm.s_parts;
+  const int total_units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
   const int k_blocks = (prm.k + BK - 1) / BK;   // dense: 128 columns per stage
   const int k_slots = (prm.k + 63) / 64;        // sparse: 64 columns per slot
 
@@ -533,21 +524,6 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             for (int j = 0; j < n / 64; ++j)
               tma_load_2d(b_dst + j * (64 * 128), &tma_b_sparse, b_full_bar(s), j * 64, kb * 64);
           }
-        } else if (prm.d_pair) {
-          // two 128-row tiles per unit, stages of 64 columns: [A tile 0 | A tile 1 | B]
-          const int kb0 = un.part * k_slots / un.parts, kb1 = (un.part + 1) * k_slots / un.parts;
-          const int nt = min(2, prm.d_tiles - tile * 2);
-          for (int kb = kb0; kb < kb1; ++kb, ++it) {
-            const int s = it % S;
-            const uint32_t ph = (it / S) & 1u;
-            if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, prm.status, 64)) { ok = false; break; }
-            const uint32_t a_dst = smem_base + s * pair_stage_bytes;
-            const uint32_t b_dst = a_dst + 2 * A_ATOM_BYTES;
-            mbar_arrive_expect_tx(full_bar(s), nt * A_ATOM_BYTES + static_cast<uint32_t>(n) * 128u);
-            for (int t = 0; t < nt; ++t)
-              tma_load_2d(a_dst + t * A_ATOM_BYTES, &tma_a, full_bar(s), kb * 64, (tile * 2 + t) * BM);
-            tma_load_2d(b_dst, &tma_b_dense, full_bar(s), kb * 64, 0);  // X^T [N rows x 64 k]
-          }
         } else {
           const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
           const bool b_mn = prm.d_b_mn;
@@ -606,25 +582,6 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             umma_commit(a_empty_bar(sa));
             umma_commit(b_empty_bar(sb));
           }
-        } else if (prm.d_pair) {
-          const int kb0 = un.part * k_slots / un.parts, kb1 = (un.part + 1) * k_slots / un.parts;
-          const int nt = min(2, prm.d_tiles - un.tile * 2);
-          for (int kb = kb0; kb < kb1; ++kb, ++it) {
-            const int s = it % S;
-            const uint32_t ph = (it / S) & 1u;
-            if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
-            tcgen05_fence_after();
-            const uint32_t a_base = smem_base + s * pair_stage_bytes;
-            const uint64_t bdesc0 = smem_desc(a_base + 2 * A_ATOM_BYTES, 16, 1024);
-            for (int t = 0; t < nt; ++t) {
-              const uint64_t adesc0 = smem_desc(a_base + t * A_ATOM_BYTES, 16, 1024);
-#pragma unroll
-              for (int ks = 0; ks < 64 / UMMA_K; ++ks)
-                umma_f16(tmem_base + static_cast<uint32_t>(t * n), desc_advance(adesc0, ks * 32),
-                         desc_advance(bdesc0, ks * 32), idesc_k, (kb != kb0 || ks != 0) ? 1u : 0u);
-            }
-            umma_commit(empty_bar(s));
-          }
         } else {
           const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
           const bool b_mn = prm.d_b_mn;
@@ -675,58 +632,53 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       }
       const int row_local = q * 32 + lane;
       const int tile_rows = sparse ? prm.s_tile_rows : BM;
+      const int row = tile * tile_rows + row_local;
+      const bool row_stored = row_local < tile_rows && row < (sparse ? prm.s_m : prm.d_m);
       __half* out = sparse ? prm.s_out : prm.d_out;
       const long long sm = sparse ? static_cast<long long>(n) : prm.d_stride_m;
       const long long sn = sparse ? 1ll : prm.d_stride_n;
-      // a dense unit of a paired launch holds two 128-row tiles in two accumulators
-      const int nt = (!sparse && prm.d_pair) ? min(2, prm.d_tiles - tile * 2) : 1;
-      for (int t = 0; t < nt; ++t) {
-        const int vt = (!sparse && prm.d_pair) ? tile * 2 + t : tile;  // 128-row tile of the output
-        const int row = vt * tile_rows + row_local;
-        const bool row_stored = row_local < tile_rows && row < (sparse ? prm.s_m : prm.d_m);
-        // partial tiles of this output tile: [part][n columns][128 rows] fp32
-        float* part_base = prm.partials == nullptr ? nullptr
-            : prm.partials + (static_cast<size_t>(sparse ? vt * prm.s_parts
-                                                          : prm.s_tiles * prm.s_parts + vt * prm.d_parts)) *
-                                 (static_cast<size_t>(BM) * n);
-        for (int c0 = 0; c0 < n; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(t * n + c0), r);
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (c0 + 32 >= n && t + 1 == nt) {  // accumulators fully read: let the next unit's MMAs start
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(accum_empty);
-          }
-          if (un.parts > 1) {
-            // partial tile stored column-major ([n][128]): the 32 lanes of a warp hold 32
-            // consecutive rows, so every store below is one coalesced 128-byte line
-            float* dst = part_base + static_cast<size_t>(un.part) * BM * n + static_cast<size_t>(c0) * BM +
-                         row_local;
+      // partial tiles of this output tile: [part][n columns][128 rows] fp32
+      float* part_base = prm.partials == nullptr ? nullptr
+          : prm.partials + (static_cast<size_t>(sparse ? tile * prm.s_parts
+                                                        : prm.s_tiles * prm.s_parts + tile * prm.d_parts)) *
+                               (static_cast<size_t>(BM) * n);
+      for (int c0 = 0; c0 < n; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 >= n) {  // accumulator fully read: let the next unit's MMAs start
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(accum_empty);
+        }
+        if (un.parts > 1) {
+          // partial tile stored column-major ([n][128]): the 32 lanes of a warp hold 32
+          // consecutive rows, so every store below is one coalesced 128-byte line
+          float* dst = part_base + static_cast<size_t>(un.part) * BM * n + static_cast<size_t>(c0) * BM +
+                       row_local;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) dst[i * BM] = __uint_as_float(r[i]);
-          } else if (row_stored) {
-            const int copies = sparse ? 0 : prm.d_num_copies;
-            for (int pe = 0; pe <= copies; ++pe) {
-              __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
-              if (sn == 1) {
-                uint4* dst = reinterpret_cast<uint4*>(o + row * sm + c0);
+          for (int i = 0; i < 32; ++i) dst[i * BM] = __uint_as_float(r[i]);
+        } else if (row_stored) {
+          const int copies = sparse ? 0 : prm.d_num_copies;
+          for (int pe = 0; pe <= copies; ++pe) {
+            __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
+            if (sn == 1) {
+              uint4* dst = reinterpret_cast<uint4*>(o + row * sm + c0);
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                  uint4 pk;
-                  __half2* h = reinterpret_cast<__half2*>(&pk);
+              for (int v = 0; v < 4; ++v) {
+                uint4 pk;
+                __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
-                  for (int i = 0; i < 4; ++i)
-                    h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]),
-                                             __uint_as_float(r[v * 8 + 2 * i + 1]));
-                  dst[v] = pk;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                  if (c0 + i < n)  // n need not be a multiple of the 32 columns read at a time
-                    o[row * sm + (c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
+                for (int i = 0; i < 4; ++i)
+                  h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]),
+                                           __uint_as_float(r[v * 8 + 2 * i + 1]));
+                dst[v] = pk;
               }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (c0 + i < n)  // n need not be a multiple of the 32 columns read at a time
+                  o[row * sm + (c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
             }
           }
         }
@@ -1113,8 +1065,7 @@ template <int ND, typename IT>
 int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMap& tbs, Params prm,
                  int stages, int ctas_per_sm, cudaStream_t stream) {
   prm.num_stages = stages;
-  size_t data = prm.d_pair ? static_cast<size_t>(stages) * (2 * A_ATOM_BYTES + prm.n * 128)
-                           : static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256);
+  size_t data = static_cast<size_t>(stages) * (A_STAGE_BYTES + prm.n * 256);
   prm.s_a_slots = 1;
   prm.s_b_slots = 1;
   prm.s_ring_rows = BM;
@@ -1142,7 +1093,7 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = smem;
   }
-  const int units = dense_groups(prm) * prm.d_parts + prm.s_tiles * prm.s_parts;
+  const int units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
   const int grid = units < sm_count() * ctas_per_sm ? units : sm_count() * ctas_per_sm;
   kern<<<grid, (kFirstDecodeWarp + ND) * 32, smem, stream>>>(ta, tbd, tbs, prm);
   int st = launch_status();
@@ -1229,14 +1180,6 @@ int bind_workspace(Params& p, int s_parts, int d_parts, void* workspace, size_t 
   return IEX_OK;
 }
 
-bool pair_mode_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("IEX_TC_PAIR");
-    return e && e[0] == '1';
-  }();
-  return on;
-}
-
 int linear_impl(int tokens, int in_features, int out_features, const void* input, const void* weight,
                 void* out, int parts, void* workspace, size_t bytes, void* stream,
                 long long ld_out = 0, void* const* copies = nullptr, int num_copies = 0) {
@@ -1263,18 +1206,11 @@ int linear_impl(int tokens, int in_features, int out_features, const void* input
   p.d_b_mn = 0;
   p.k = in_features;
   p.n = tokens;
-  // From 128 tokens on the X tile of a stage is as large as the weight tile: two weight
-  // tiles then share it (two accumulators of `tokens` TMEM columns each).
-  p.d_pair = (pair_mode_enabled() && tokens >= 128 && 2 * tokens <= 512 && p.d_tiles >= 2) ? 1 : 0;
-  p.tmem_cols = tmem_cols_for(p.d_pair ? 2 * tokens : tokens);
+  p.tmem_cols = tmem_cols_for(tokens);
   p.status = status_word();
   st = bind_workspace(p, 1, parts, workspace, bytes);
   if (st) return st;
-  int stages = dense_stages(tokens, kMaxStages);
-  if (p.d_pair) {
-    stages = kDataBudget / (2 * A_ATOM_BYTES + tokens * 128);
-    stages = stages > kMaxStages ? kMaxStages : stages;
-  }
+  const int stages = dense_stages(tokens, kMaxStages);
   if (stages < 2) return IEX_ERR_UNSUPPORTED;
   return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
 }
