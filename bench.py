@@ -588,6 +588,24 @@ def _time_us(fn, iters=20, warmup=4):
     return e0.elapsed_time(e1) / iters * 1e3
 
 
+def _cold_launch_us(fn, reps=9):
+    """Median time of ONE launch with nothing of its operands in L2: a 256 MB buffer is written
+    before every launch, the device is idle when the launch is enqueued."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for i in range(reps):
+        flush.fill_(i & 1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    del flush
+    return statistics.median(times)
+
+
 def other_configs_section(dev) -> dict:
     """Configurations 1 and 3 (small SpMMs: cold single launch and warm rotation over > L2)."""
     from intrasm_engine_b200 import _lib, synthetic as syn
@@ -611,7 +629,8 @@ def other_configs_section(dev) -> dict:
 
     us = _time_us(c1, iters=128, warmup=64)
     by = syn.spmm_bytes(1024, 1024, 256, a.nnz, 4, 4)
-    out["cfg1_spmm_fp32"] = {"us_per_launch_rotating": us, "gflops": syn.spmm_flops(a.nnz, 256) / us / 1e3,
+    out["cfg1_spmm_fp32"] = {"us_per_launch_rotating": us, "us_cold_single_launch": _cold_launch_us(c1),
+                             "gflops": syn.spmm_flops(a.nnz, 256) / us / 1e3,
                              "frac_hbm": by / us / 1e3 / peak, "bytes": by}
     # ---- config 3: the whole fp16 sweep (int16 indices), both kernels, and what the cost model
     # of intrasm_engine_b200/pytorch/tuning.py would have picked
@@ -640,6 +659,10 @@ def other_configs_section(dev) -> dict:
 
                 t_simt = _time_us(simt, iters=96, warmup=48)
                 t_tc = _time_us(tc, iters=96, warmup=48)
+                cold = {}
+                if (rows, cols, sparsity, n) in ((512, 512, 0.9, 256), (2048, 512, 0.7, 128), (512, 2048, 0.95, 128)):
+                    cold = {"cuda_core_us_cold_single_launch": round(_cold_launch_us(simt, 5), 2),
+                            "tensor_core_us_cold_single_launch": round(_cold_launch_us(tc, 5), 2)}
                 pick = tuning.choose_spmm_kernel(rows, cols, n, a3.nnz)
                 t_pick = t_tc if pick == "tensor_core" else t_simt
                 best = min(t_simt, t_tc)
@@ -648,7 +671,7 @@ def other_configs_section(dev) -> dict:
                 sweep[f"{rows}x{cols}_s{sparsity}_n{n}"] = {
                     "nnz": a3.nnz, "cuda_core_us": round(t_simt, 2), "tensor_core_us": round(t_tc, 2),
                     "model_picks": pick, "gflops_best": round(syn.spmm_flops(a3.nnz, n) / best / 1e3, 1),
-                    "frac_hbm_best": round(per_copy / best / 1e3 / peak, 4)}
+                    "frac_hbm_best": round(per_copy / best / 1e3 / peak, 4), **cold}
                 del c3s
     sweep["summary"] = {"cases": len(regret), "model_picked_the_faster_kernel": hits,
                         "mean_time_vs_best": round(sum(regret) / len(regret), 3),
