@@ -123,6 +123,13 @@ IEX_API int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_off
                             const void* column_indices, int index_bits, const void* values,
                             const void* dense, void* out, void* stream);
 
+/* The same with the reference's bias + ReLU epilogue (my_sputnik::CudaSpmmBiasRelu5,
+ * extensions.h:30; sputnik_spmm.cu.inc:273-282): out[r, :] = relu(sum + bias[r]); bias fp32[m],
+ * NULL for the plain product. */
+IEX_API int iex_spmm_f16_tc_bias_relu(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                                      const void* column_indices, int index_bits, const void* values,
+                                      const void* dense, const float* bias, void* out, void* stream);
+
 /* Fused sparse || dense layer: ONE launch computes
  *     out_sparse[r, t] = sum_p values[p] * x[col[p], t]        (CSR W_sparse [m_sparse, k])
  *     out_dense        = weight [m_dense, k] times x           (dense)

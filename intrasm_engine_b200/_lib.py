@@ -37,6 +37,9 @@ SIGNATURES = {
     # m k n nnz row_offsets cols index_bits values dense out stream
     "iex_spmm_f16_tc": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
                                 c_ptr, c_ptr]),
+    # m k n nnz row_offsets cols index_bits values dense bias out stream
+    "iex_spmm_f16_tc_bias_relu": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
+                                          c_ptr, c_ptr, c_ptr]),
     # m_sparse m_dense k n nnz row_offsets cols index_bits values weight x out_sparse out_dense
     # dense_out_tokens_major stream
     "iex_fused_spmm_linear_f16": (c_int, [c_int, c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int,

@@ -74,6 +74,7 @@ struct Params {
   const int* s_row_offsets;
   const void* s_cols;
   const __half* s_values;
+  const float* s_bias;  // optional: out = relu(sum + bias[row]) for the sparse branch
   // shared
   int k, n;
   int num_stages, tmem_cols;
@@ -659,6 +660,11 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 #pragma unroll
           for (int i = 0; i < 32; ++i) dst[i * BM] = __uint_as_float(r[i]);
         } else if (row_stored) {
+          if (sparse && prm.s_bias != nullptr) {  // bias + ReLU epilogue of the sparse branch
+            const float bias = __ldg(prm.s_bias + row);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]) + bias, 0.f));
+          }
           const int copies = sparse ? 0 : prm.d_num_copies;
           for (int pe = 0; pe <= copies; ++pe) {
             __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
@@ -1218,7 +1224,8 @@ int linear_impl(int tokens, int in_features, int out_features, const void* input
 int fused_impl(int m_sparse, int m_dense, int k, int n, int nnz, const int32_t* row_offsets,
                const void* column_indices, int index_bits, const void* values, const void* weight,
                const void* x, void* out_sparse, void* out_dense, int dense_out_tokens_major,
-               int sparse_parts, int dense_parts, void* workspace, size_t bytes, void* stream) {
+               int sparse_parts, int dense_parts, void* workspace, size_t bytes, void* stream,
+               const float* sparse_bias = nullptr) {
   if (m_dense < 0 || m_sparse < 0) return IEX_ERR_BAD_ARG;
   int st;
   if (m_sparse > 0) {
@@ -1258,6 +1265,7 @@ int fused_impl(int m_sparse, int m_dense, int k, int n, int nnz, const int32_t* 
   p.s_row_offsets = row_offsets;
   p.s_cols = column_indices;
   p.s_values = static_cast<const __half*>(values);
+  p.s_bias = sparse_bias;
   p.k = k;
   p.n = n;
   p.tmem_cols = tmem_cols_for(n);
@@ -1298,6 +1306,14 @@ extern "C" int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_
   if (m == 0) return IEX_OK;
   return fused_impl(m, 0, k, n, nnz, row_offsets, column_indices, index_bits, values, nullptr, dense, out,
                     nullptr, 1, 1, 1, nullptr, 0, stream);
+}
+
+extern "C" int iex_spmm_f16_tc_bias_relu(int m, int k, int n, int nnz, const int32_t* row_offsets,
+                                         const void* column_indices, int index_bits, const void* values,
+                                         const void* dense, const float* bias, void* out, void* stream) {
+  if (m == 0) return IEX_OK;
+  return fused_impl(m, 0, k, n, nnz, row_offsets, column_indices, index_bits, values, nullptr, dense, out,
+                    nullptr, 1, 1, 1, nullptr, 0, stream, bias);
 }
 
 extern "C" int iex_spmm_f16_tc_splitk(int m, int k, int n, int nnz, const int32_t* row_offsets,

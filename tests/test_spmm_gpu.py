@@ -155,8 +155,9 @@ def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n, idx):
     tref = oracle.torch_spmm(a.row_offsets, a.column_indices, a.values, b, rows)
     assert G.close(got, tref, 1e-2, 1e-2)
     tc = torch.empty((rows, n), dtype=torch.float16, device=G.DEV)
+    db = G.dev(b)  # kept alive: the call is asynchronous
     _lib.call("iex_spmm_f16_tc", rows, cols, n, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
-              16 if idx == np.int16 else 32, da.values.data_ptr(), G.dev(b).data_ptr(), tc.data_ptr(),
+              16 if idx == np.int16 else 32, da.values.data_ptr(), db.data_ptr(), tc.data_ptr(),
               G.stream_ptr())
     assert G.close(tc.cpu().numpy(), ref, 1e-2, 1e-2)
     assert _lib.lib.iex_last_device_status(1) == 0

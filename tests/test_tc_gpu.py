@@ -124,6 +124,32 @@ def test_spmm_tc_shapes(oracle, m, k, n, density, idx):
     _status_clean()
 
 
+@pytest.mark.parametrize("m,k,n,idx", [(300, 520, 64, np.int16), (1100, 1024, 128, np.int32)])
+def test_spmm_tc_bias_relu(oracle, m, k, n, idx):
+    """Bias + ReLU epilogue of the tensor-core SpMM against the oracle's (fp32 bias per row)."""
+    rng = np.random.default_rng(m + n)
+    mask = rng.random((m, k)) < 0.3
+    a = syn.csr_from_mask(mask, rng=rng, std=0.05, dtype=np.float16, index_dtype=idx)
+    b = rng.standard_normal((k, n)).astype(np.float16)
+    bias = rng.standard_normal(m).astype(np.float32)
+    da = G.DevCSR(a)
+    db, dbias = G.dev(b), G.dev(bias)  # kept alive: the calls below are asynchronous
+    out = torch.empty((m, n), dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_spmm_f16_tc_bias_relu", m, k, n, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
+              16 if idx == np.int16 else 32, da.values.data_ptr(), db.data_ptr(), dbias.data_ptr(),
+              out.data_ptr(), G.stream_ptr())
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, m, bias=bias)[0]
+    got = out.cpu().numpy()
+    assert G.close(got, ref, RTOL, RTOL), G.max_violation(got, ref, RTOL, RTOL)
+    assert (got >= 0).all() and (got == 0).any()
+    # no bias pointer: the plain product
+    _lib.call("iex_spmm_f16_tc_bias_relu", m, k, n, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
+              16 if idx == np.int16 else 32, da.values.data_ptr(), db.data_ptr(), None, out.data_ptr(),
+              G.stream_ptr())
+    assert torch.equal(out, _spmm_tc(da, db))
+    _status_clean()
+
+
 def test_spmm_tc_matches_cuda_core_kernel():
     """Two independent kernels (CUDA cores, bit-exact with the oracle; tensor cores) agree."""
     a, b = syn.pruned_sweep_case(7, 2048, 512, 0.7, 128)
