@@ -21,6 +21,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/library.h>
 
+#include <algorithm>
 #include <tuple>
 
 #include "iex_b200.h"
@@ -161,9 +162,25 @@ at::Tensor linear_fp16(const at::Tensor& input, const at::Tensor& weight) {
   TORCH_CHECK(input.scalar_type() == at::kHalf && weight.scalar_type() == at::kHalf,
               "input and weight must be float16");
   c10::cuda::CUDAGuard guard(input.device());
-  at::Tensor out = at::empty({input.size(0), weight.size(0)}, input.options());
-  check_status(iex_linear_f16(input.size(0), input.size(1), weight.size(0), input.data_ptr(),
-                              weight.data_ptr(), out.data_ptr(), stream_of(input)),
+  const int64_t tokens = input.size(0), out_features = weight.size(0);
+  at::Tensor out = at::empty({tokens, out_features}, input.options());
+  // A weight with few 128-row tiles would leave most SMs without work: split every tile's K
+  // range over about 128 / tiles CTAs (measured optimum on B200: 32 tiles -> 4 parts,
+  // 4 tiles -> 16).  The partial tiles live in a scratch tensor of the caching allocator.
+  const int64_t tiles = (out_features + 127) / 128;
+  const int parts = tiles > 0 ? static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(16, 128 / tiles))) : 1;
+  if (parts > 1 && tokens % 32 == 0 && input.size(1) >= 128 * parts) {
+    const size_t need = iex_tc_workspace_bytes(0, 1, static_cast<int>(out_features), parts,
+                                               static_cast<int>(tokens));
+    at::Tensor scratch = at::empty({static_cast<int64_t>(need)}, input.options().dtype(at::kByte));
+    check_status(iex_linear_f16_splitk(tokens, input.size(1), out_features, input.data_ptr(),
+                                       weight.data_ptr(), out.data_ptr(), parts, scratch.data_ptr(), need,
+                                       stream_of(input)),
+                 "iex_linear_f16_splitk");
+    return out;
+  }
+  check_status(iex_linear_f16(tokens, input.size(1), out_features, input.data_ptr(), weight.data_ptr(),
+                              out.data_ptr(), stream_of(input)),
                "iex_linear_f16");
   return out;
 }

@@ -92,6 +92,21 @@ def test_linear_writes_nothing_past_the_output(tokens):
     _status_clean()
 
 
+@pytest.mark.parametrize("tokens,cin,cout", [(64, 4096, 512), (256, 11008, 1024), (48, 4096, 512), (64, 256, 384)])
+def test_linear_op_splits_few_tile_weights(tokens, cin, cout):
+    """torch.ops.iex_ops.linear_fp16 spreads a weight of few 128-row tiles over the SMs by
+    itself (split-K with a scratch tensor from the caching allocator) where the shape allows;
+    either way the result is the product."""
+    rng = np.random.default_rng(tokens + cout)
+    x = G.dev(rng.standard_normal((tokens, cin)).astype(np.float16))
+    w = G.dev((rng.standard_normal((cout, cin)) * 0.05).astype(np.float16))
+    out = torch.ops.iex_ops.linear_fp16(x, w)
+    ref = x.float() @ w.float().t()
+    assert torch.allclose(out.float(), ref, rtol=1e-2, atol=1e-2 * float(ref.abs().max()))
+    assert torch.allclose(out.float(), _linear(x, w).float(), rtol=2e-3, atol=2e-3 * float(ref.abs().max()))
+    _status_clean()
+
+
 def test_linear_rejects_unsupported():
     x = torch.zeros((20, 64), dtype=torch.float16, device=G.DEV)
     w = torch.zeros((64, 64), dtype=torch.float16, device=G.DEV)
