@@ -48,6 +48,23 @@ def test_sddmm_shapes(oracle, m, n, k, density, batch):
     assert G.close(got, exact, 1e-5, 1e-5), G.max_violation(got, exact, 1e-5, 1e-5)
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_sddmm_random_shapes(oracle, seed):
+    """Seeded random shapes: ragged rows (empty to full), every k alignment class, batches."""
+    rng = np.random.default_rng(500 + seed)
+    m, n = int(rng.integers(1, 400)), int(rng.integers(1, 600))
+    k = int(rng.choice([1, 3, 4, 8, 20, 32, 36, 64, 100, 128, 200, 260]))
+    batch = int(rng.integers(1, 4))
+    row_density = rng.choice([0.0, 0.02, 0.2, 1.0], size=m, p=[0.15, 0.4, 0.35, 0.1])
+    mask = syn.csr_from_mask(rng.random((m, n)) < row_density[:, None], rng=rng)
+    lhs = rng.standard_normal((batch, m, k)).astype(np.float32)
+    rhs = rng.standard_normal((batch, n, k)).astype(np.float32)
+    got = G.sddmm_f32(G.DevCSR(mask), G.dev(lhs), G.dev(rhs)).cpu().numpy()
+    exact = oracle.sddmm(lhs, rhs, mask.row_indices, mask.row_offsets, mask.column_indices, f64=True)
+    assert got.shape == exact.shape
+    assert G.close(got, exact, 1e-5, 1e-5), (m, n, k, batch, G.max_violation(got, exact, 1e-5, 1e-5))
+
+
 def test_sddmm_accumulate_and_determinism(oracle):
     mask, q, k, _ = syn.sddmm_chain_case(2, 128, 160, 64, 0.1)
     dm = G.DevCSR(mask)

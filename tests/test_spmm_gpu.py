@@ -128,6 +128,30 @@ def test_spmm_f32_bias_relu_accumulate_batch(oracle):
     np.testing.assert_array_equal(got, ref)
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_spmm_random_shapes(oracle, seed):
+    """Seeded random shapes for the CUDA-core kernels: ragged rows, every n (odd ones too),
+    batches, bias; fp32 and fp16 (both index widths) bit for bit against the oracle."""
+    rng = np.random.default_rng(700 + seed)
+    m, k = int(rng.integers(1, 500)), int(rng.integers(1, 900))
+    n = int(rng.choice([1, 3, 8, 16, 24, 33, 64, 100, 128, 256, 264]))
+    batch = int(rng.integers(1, 3))
+    row_density = rng.choice([0.0, 0.02, 0.2, 1.0], size=m, p=[0.15, 0.4, 0.35, 0.1])
+    mask = rng.random((m, k)) < row_density[:, None]
+    a = syn.csr_from_mask(mask, rng=rng)
+    dense = rng.standard_normal((batch, k, n)).astype(np.float32)
+    bias = rng.standard_normal(m).astype(np.float32) if seed % 2 else None
+    got = G.spmm_f32(G.DevCSR(a), G.dev(dense), bias=None if bias is None else G.dev(bias)).cpu().numpy()
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, dense, m, bias=bias)
+    np.testing.assert_array_equal(got, ref)
+    idx = np.int16 if seed % 3 else np.int32
+    ah = syn.csr_from_mask(mask, rng=rng, std=0.05, dtype=np.float16, index_dtype=idx)
+    dh = dense.astype(np.float16)
+    goth = G.spmm_f16(G.DevCSR(ah), G.dev(dh), bias=None if bias is None else G.dev(bias)).cpu().numpy()
+    refh = oracle.spmm(ah.row_indices, ah.values, ah.row_offsets, ah.column_indices, dh, m, bias=bias)
+    np.testing.assert_array_equal(goth, refh.astype(np.float16))
+
+
 def test_spmm_cfg1_full_size(oracle):
     """Benchmark configuration 1: 1024x1024 at 90 % sparsity times 1024x256, fp32."""
     for seed in (0, 1):

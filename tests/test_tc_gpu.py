@@ -165,6 +165,34 @@ def test_spmm_tc_bias_relu(oracle, m, k, n, idx):
     _status_clean()
 
 
+@pytest.mark.parametrize("seed", range(48))
+def test_spmm_tc_random_shapes(oracle, seed):
+    """Seeded random shapes and row patterns for the tensor-core SpMM and the fused launch:
+    rows that are empty, nearly empty, half full or full in one matrix, K that is not a multiple
+    of the 64-column slots, every token count and both index widths."""
+    rng = np.random.default_rng(1000 + seed)
+    m = int(rng.integers(1, 700))
+    k = int(rng.integers(1, 257)) * 8
+    n = int(rng.choice([64, 128, 192, 256]))
+    idx = np.int16 if rng.random() < 0.5 else np.int32
+    row_density = rng.choice([0.0, 0.01, 0.1, 0.5, 1.0], size=m, p=[0.1, 0.2, 0.3, 0.3, 0.1])
+    mask = rng.random((m, k)) < row_density[:, None]
+    a = syn.csr_from_mask(mask, rng=rng, std=0.05, dtype=np.float16, index_dtype=idx)
+    b = rng.standard_normal((k, n)).astype(np.float16)
+    da, db = G.DevCSR(a), G.dev(b)
+    got = _spmm_tc(da, db)
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, m)[0]
+    assert G.close(got.cpu().numpy(), ref, RTOL, RTOL), (m, k, n, idx)
+    if seed % 3 == 0:  # the same sparse matrix beside a dense one in the fused launch
+        md = int(rng.integers(1, 40)) * 8
+        w = (rng.standard_normal((md, k)) * 0.05).astype(np.float16)
+        out_s, out_d = _fused(da, G.dev(w), db)
+        assert torch.equal(out_s, got)
+        ref_d = b.astype(np.float32).T @ w.astype(np.float32).T
+        assert G.close(out_d.cpu().numpy(), ref_d, RTOL, RTOL), (m, md, k, n)
+    _status_clean()
+
+
 def test_spmm_tc_matches_cuda_core_kernel():
     """Two independent kernels (CUDA cores, bit-exact with the oracle; tensor cores) agree."""
     a, b = syn.pruned_sweep_case(7, 2048, 512, 0.7, 128)
