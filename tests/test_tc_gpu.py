@@ -107,6 +107,35 @@ def test_linear_op_splits_few_tile_weights(tokens, cin, cout):
     _status_clean()
 
 
+@pytest.mark.parametrize("seed", range(32))
+def test_linear_random_shapes(seed):
+    """Seeded random shapes for the dense linear, plain and split-K (workspace and built-in
+    scratch), against the fp32 product."""
+    rng = np.random.default_rng(300 + seed)
+    tokens = int(rng.integers(1, 17)) * 16
+    cin = int(rng.integers(1, 400)) * 8
+    cout = int(rng.integers(1, 1500))
+    x = G.dev(rng.standard_normal((tokens, cin)).astype(np.float16))
+    w = G.dev((rng.standard_normal((cout, cin)) * 0.05).astype(np.float16))
+    ref = (x.float() @ w.float().t()).cpu().numpy()
+    got = _linear(x, w)
+    assert G.close(got.cpu().numpy(), ref, RTOL, RTOL), (tokens, cin, cout)
+    if tokens % 32 == 0:
+        parts = int(rng.integers(2, 9))
+        need = _lib.lib.iex_tc_workspace_bytes(0, 1, cout, parts, tokens)
+        ws = _workspace(need)
+        out = torch.zeros((tokens, cout), dtype=torch.float16, device=G.DEV)
+        _lib.call("iex_linear_f16_splitk", tokens, cin, cout, x.data_ptr(), w.data_ptr(), out.data_ptr(),
+                  parts, ws.data_ptr(), ws.numel(), G.stream_ptr())
+        assert G.close(out.cpu().numpy(), ref, RTOL, RTOL), (tokens, cin, cout, parts)
+        if need <= _lib.lib.iex_static_workspace_capacity():
+            out2 = torch.zeros_like(out)
+            _lib.call("iex_linear_f16_splitk_static", tokens, cin, cout, x.data_ptr(), w.data_ptr(),
+                      out2.data_ptr(), parts, G.stream_ptr())
+            assert torch.equal(out2, out)
+    _status_clean()
+
+
 def test_linear_rejects_unsupported():
     x = torch.zeros((20, 64), dtype=torch.float16, device=G.DEV)
     w = torch.zeros((64, 64), dtype=torch.float16, device=G.DEV)
