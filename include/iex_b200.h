@@ -216,6 +216,15 @@ IEX_API int iex_linear_f16_splitk_gather(int tokens, int in_features, int out_fe
  * counterpart in the reference. */
 IEX_API int iex_peer_barrier(void* const* signals, int world, int rank, void* stream);
 
+/* The same barrier with the caller's own limit on the wait: max_polls polls of about 100 ns
+ * each (0 = the default, also the upper limit).  A rank that knows a peer may have left (a
+ * host-side heartbeat went missing) can bound the damage to microseconds, and a test can make
+ * the wait run out on purpose -- a signal word that nobody writes -- to see the failure path:
+ * the kernel returns, IEX_ERR_TIMEOUT is left in the status word, and the context stays
+ * usable.  No counterpart in the reference. */
+IEX_API int iex_peer_barrier_bounded(void* const* signals, int world, int rank, unsigned max_polls,
+                                     void* stream);
+
 /* Dense fp16 copy of a CSR matrix: out [m, k] row-major, zeros where nothing is stored.
  * The device-side counterpart of the CSR <-> dense conversions the reference delegates to
  * xformers (intrasm_engine/pytorch/utils.py:143-153); used to hand an activation CSR to the
@@ -239,6 +248,26 @@ IEX_API int iex_dense_to_csr_count(int m, int k, const void* dense, int value_bi
 IEX_API int iex_dense_to_csr_fill(int m, int k, const void* dense, int value_bits, int relu,
                                   const int32_t* row_offsets, void* values, void* column_indices,
                                   int index_bits, void* stream);
+
+/* CSR sanity check on the device.  The reference's launchers trust their index arrays
+ * (intrasm_engine/pytorch/csrc/extensions/sputnik_kernels.cpp:41-91 checks shapes and
+ * dtypes only); the kernels here gather dense rows at column_indices unchecked, so a caller
+ * that cannot vouch for its CSR runs this first.  Writes 0 to *result (a device word the
+ * caller owns) when the matrix is well formed, else the OR of the IEX_CSR_* bits below.
+ * row_indices may be NULL (not checked); require_ascending != 0 also demands strictly
+ * ascending columns inside every row, the precondition of the tensor-core SpMM.  The call
+ * enqueues a memset and one kernel on `stream`; the caller reads *result after its own
+ * synchronisation.  Duplicate entries in row_indices are not detected. */
+#define IEX_CSR_BAD_FIRST_OFFSET 1       /* row_offsets[0] != 0                        */
+#define IEX_CSR_BAD_LAST_OFFSET 2        /* row_offsets[m] != nnz                      */
+#define IEX_CSR_OFFSETS_NOT_MONOTONE 4   /* a row ends before it begins                */
+#define IEX_CSR_COLUMN_OUT_OF_RANGE 8    /* a column index outside [0, k)              */
+#define IEX_CSR_COLUMNS_NOT_ASCENDING 16 /* columns of a row not strictly ascending    */
+#define IEX_CSR_BAD_ROW_INDEX 32         /* a row_indices entry outside [0, m)         */
+IEX_API int iex_csr_validate(int m, int k, int nnz, const int32_t* row_offsets,
+                             const void* column_indices, int index_bits,
+                             const int32_t* row_indices, int require_ascending,
+                             int32_t* result, void* stream);
 
 /* Last device-side failure recorded by any kernel of this library (0 = none).
  * Synchronises the device.  clear != 0 resets the word. */

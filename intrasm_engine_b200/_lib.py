@@ -61,11 +61,15 @@ SIGNATURES = {
                                              c_int, c_ll, c_ll, c_int, c_ptr, c_size, c_ptr]),
     # signals world rank stream
     "iex_peer_barrier": (c_int, [ctypes.POINTER(c_ptr), c_int, c_int, c_ptr]),
+    # signals world rank max_polls stream
+    "iex_peer_barrier_bounded": (c_int, [ctypes.POINTER(c_ptr), c_int, c_int, ctypes.c_uint, c_ptr]),
     # m k dense value_bits relu row_offsets row_indices stream
     "iex_dense_to_csr_count": (c_int, [c_int, c_int, c_ptr, c_int, c_int, c_ptr, c_ptr, c_ptr]),
     # m k dense value_bits relu row_offsets values cols index_bits stream
     "iex_dense_to_csr_fill": (c_int, [c_int, c_int, c_ptr, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
     "iex_csr_to_dense_f16": (c_int, [c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr]),
+    # m k nnz row_offsets cols index_bits row_indices require_ascending result stream
+    "iex_csr_validate": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_int, c_ptr, c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)
     "iex_graph_create": (c_ptr, []),

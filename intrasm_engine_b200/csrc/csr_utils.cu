@@ -137,8 +137,70 @@ csr_to_dense_f16_kernel(int m, int k, const int* __restrict__ row_offsets, const
   }
 }
 
+// CSR sanity check.  Threads stride over rows (offset rules, row order entries) and over
+// nonzeros (column range, ascending order inside a row: position p belongs to a row boundary
+// exactly when some offset equals p, which a binary search over row_offsets answers).
+// Violations are OR-ed into one device word.
+template <typename IT>
+__global__ void __launch_bounds__(256)
+csr_validate_kernel(int m, int k, int nnz, const int* __restrict__ row_offsets, const IT* __restrict__ cols,
+                    const int* __restrict__ row_indices, int require_ascending, int* __restrict__ result) {
+  const int tid = blockIdx.x * blockDim.x + threadIdx.x;
+  const int nthreads = gridDim.x * blockDim.x;
+  int bad = 0;
+  if (tid == 0) {
+    if (row_offsets[0] != 0) bad |= IEX_CSR_BAD_FIRST_OFFSET;
+    if (row_offsets[m] != nnz) bad |= IEX_CSR_BAD_LAST_OFFSET;
+  }
+  for (int r = tid; r < m; r += nthreads) {
+    const int a = row_offsets[r], b = row_offsets[r + 1];
+    if (b < a || a < 0 || b > nnz) bad |= IEX_CSR_OFFSETS_NOT_MONOTONE;
+    if (row_indices != nullptr) {
+      const int v = row_indices[r];
+      if (v < 0 || v >= m) bad |= IEX_CSR_BAD_ROW_INDEX;
+    }
+  }
+  for (int p = tid; p < nnz; p += nthreads) {
+    const int c = to_index(cols[p]);
+    if (c < 0 || c >= k) bad |= IEX_CSR_COLUMN_OUT_OF_RANGE;
+    if (require_ascending && p > 0) {
+      // is p the first nonzero of a row?  largest r with row_offsets[r] <= p ...
+      int lo = 0, hi = m;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (row_offsets[mid] <= p) lo = mid; else hi = mid - 1;
+      }
+      // ... starts the row holding p; p continues a row when that offset is below p
+      if (row_offsets[lo] < p && to_index(cols[p - 1]) >= c) bad |= IEX_CSR_COLUMNS_NOT_ASCENDING;
+    }
+  }
+  if (bad) atomicOr(result, bad);
+}
+
 }  // namespace
 }  // namespace iex
+
+extern "C" int iex_csr_validate(int m, int k, int nnz, const int32_t* row_offsets, const void* column_indices,
+                                int index_bits, const int32_t* row_indices, int require_ascending,
+                                int32_t* result, void* stream) {
+  using namespace iex;
+  if (m < 0 || k < 0 || nnz < 0 || (index_bits != 16 && index_bits != 32)) return IEX_ERR_BAD_ARG;
+  if (!row_offsets || !result || (nnz > 0 && !column_indices)) return IEX_ERR_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(result, 0, sizeof(int32_t), s);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const long long work = static_cast<long long>(nnz) > m ? nnz : m;
+  long long blocks = (work + 255) / 256;
+  blocks = blocks < 1 ? 1 : (blocks > 8 * kNumSMs ? 8 * kNumSMs : blocks);
+  if (index_bits == 16)
+    csr_validate_kernel<uint16_t><<<static_cast<int>(blocks), 256, 0, s>>>(
+        m, k, nnz, row_offsets, static_cast<const uint16_t*>(column_indices), row_indices, require_ascending,
+        result);
+  else
+    csr_validate_kernel<int><<<static_cast<int>(blocks), 256, 0, s>>>(
+        m, k, nnz, row_offsets, static_cast<const int*>(column_indices), row_indices, require_ascending, result);
+  return launch_status();
+}
 
 extern "C" int iex_csr_to_dense_f16(int m, int k, const int32_t* row_offsets, const void* column_indices,
                                     int index_bits, const void* values, void* out, void* stream) {

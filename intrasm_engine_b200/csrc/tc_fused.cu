@@ -957,8 +957,9 @@ struct PeerSignals {
   uint32_t* sig[kMaxPeers];
   int world, rank;
   int* status;
+  uint32_t max_polls;  // polls of ~100 ns each before the wait gives up
 };
-constexpr uint32_t kPeerSpinLimit = 1u << 22;  // polls of ~100 ns each
+constexpr uint32_t kPeerSpinLimit = 1u << 22;  // default limit: a fraction of a second
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerSignals ps) {
   __shared__ uint32_t epoch_s;
@@ -975,7 +976,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerSignals ps) 
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ps.sig[q] + ps.rank), "r"(epoch) : "memory");
     const uint32_t* src = ps.sig[ps.rank] + q;
     bool arrived = false;
-    for (uint32_t i = 0; i < kPeerSpinLimit; ++i) {
+    for (uint32_t i = 0; i < ps.max_polls; ++i) {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
       if (static_cast<int>(v - epoch) >= 0) { arrived = true; break; }
@@ -1022,15 +1023,30 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long cols,
   return r == CUDA_SUCCESS ? IEX_OK : IEX_ERR_DRIVER;
 }
 
+// Per-device host state.  One process may drive several GPUs (the torch operators accept
+// tensors on any device), and both the SM count and the opt-in dynamic shared-memory limit of
+// a kernel belong to a device, so they are remembered per device index under a mutex.
+constexpr int kMaxDevices = 64;
+std::mutex g_device_mutex;
+int g_sm_count[kMaxDevices] = {};
+
+int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
 int sm_count() {
-  static int sms = [] {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return kNumSMs;
+  const int dev = current_device();
+  if (dev < 0) return kNumSMs;
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  if (g_sm_count[dev] == 0) {
+    int v = 0;
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-      return kNumSMs;
-    return v;
-  }();
-  return sms;
+      v = kNumSMs;
+    g_sm_count[dev] = v;
+  }
+  return g_sm_count[dev];
 }
 
 int* status_word() {
@@ -1092,12 +1108,17 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
   prm.bar_offset = static_cast<uint32_t>(data);
   const size_t smem = 1024 + data + kBarBytes;
   auto kern = tc_units_kernel<ND, IT>;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = smem;
+  {
+    // high-water mark of the opt-in shared-memory size, per device and per instantiation
+    static size_t configured[kMaxDevices] = {};
+    const int dev = current_device();
+    std::lock_guard<std::mutex> lock(g_device_mutex);
+    if (dev < 0 || smem > configured[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (dev >= 0) configured[dev] = smem;
+    }
   }
   const int units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
   const int grid = units < sm_count() * ctas_per_sm ? units : sm_count() * ctas_per_sm;
@@ -1126,6 +1147,11 @@ using namespace iex::tc;
 
 extern "C" int iex_last_device_status(int clear) {
   int v = 0;
+  // Work on non-blocking streams (torch's pool streams, graph replays) is not ordered before a
+  // symbol copy, so wait for the whole device first: a kernel still running could record a
+  // failure after the read.
+  const cudaError_t sync = cudaDeviceSynchronize();
+  if (sync != cudaSuccess) return static_cast<int>(sync);
   if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return IEX_ERR_DRIVER;
   if (clear && v != 0) {
     int z = 0;
@@ -1359,7 +1385,6 @@ extern "C" int iex_fused_spmm_linear_f16_splitk(int m_sparse, int m_dense, int k
 namespace {
 
 constexpr size_t kStaticWorkspaceBytes = size_t(8) << 20;  // 8 MiB per device
-constexpr int kMaxDevices = 64;
 
 }  // namespace
 
@@ -1434,7 +1459,8 @@ extern "C" int iex_linear_f16_splitk_gather(int tokens, int in_features, int out
                      stream, ld_out, copies, n);
 }
 
-extern "C" int iex_peer_barrier(void* const* signals, int world, int rank, void* stream) {
+extern "C" int iex_peer_barrier_bounded(void* const* signals, int world, int rank, unsigned max_polls,
+                                        void* stream) {
   if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || !signals) return IEX_ERR_BAD_ARG;
   PeerSignals ps{};
   for (int r = 0; r < world; ++r) {
@@ -1444,6 +1470,11 @@ extern "C" int iex_peer_barrier(void* const* signals, int world, int rank, void*
   ps.world = world;
   ps.rank = rank;
   ps.status = status_word();
+  ps.max_polls = max_polls == 0 ? kPeerSpinLimit : (max_polls > kPeerSpinLimit ? kPeerSpinLimit : max_polls);
   peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps);
   return launch_status();
+}
+
+extern "C" int iex_peer_barrier(void* const* signals, int world, int rank, void* stream) {
+  return iex_peer_barrier_bounded(signals, world, rank, 0, stream);
 }

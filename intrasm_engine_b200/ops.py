@@ -15,6 +15,11 @@ module only loads it.  Operators:
   fused_spmm_linear_half(x, row_offsets, values, column_indices, m, weight)
                                                                 (A_csr @ x, (weight @ x).T)
   csr_to_dense_half(row_offsets, values, column_indices, m, k)  dense copy of a CSR matrix
+  validate_csr(row_offsets, column_indices, m, k, require_ascending) -> int
+                                                                0, or IEX_CSR_* bits
+With ``IEX_VALIDATE_CSR=1`` in the environment every sparse operator runs that check on its
+arguments first and raises on a malformed matrix (debugging aid; one extra kernel and a
+synchronisation per call).
 
 All are implemented for the CUDA dispatch key only: there is no CPU path.
 """
@@ -44,4 +49,5 @@ OP_NAMES = (
     "spmm_tc_half",
     "fused_spmm_linear_half",
     "csr_to_dense_half",
+    "validate_csr",
 )

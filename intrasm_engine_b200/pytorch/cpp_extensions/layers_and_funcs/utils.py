@@ -36,7 +36,10 @@ class captured:
     bracket the reference writes out around every op call (sputnik.py:58-66)."""
 
     def __init__(self, constructor, stream_idx: int, enabled: bool):
-        self.constructor, self.stream_idx, self.enabled = constructor, stream_idx, enabled
+        # no constructor to record into (e.g. a backward pass without a backward constructor):
+        # the enclosed calls simply run
+        self.constructor, self.stream_idx = constructor, stream_idx
+        self.enabled = bool(enabled) and constructor is not None
         self._stream = None
 
     def __enter__(self):

@@ -194,8 +194,11 @@ def _fusable(args, fwd_kwargs) -> bool:
     k, n = b.shape
     return (b.dtype == torch.float16 and values.dtype == torch.float16 and weight.dtype == torch.float16
             and b.is_contiguous() and inp.shape == (n, k) and inp.data_ptr() == b.data_ptr()
-            and inp.stride() == (1, n) and n % 64 == 0 and n <= 128 and k % 8 == 0
-            and weight.is_contiguous() and weight.size(1) == k)
+            and inp.stride() == (1, n) and n % 64 == 0 and n <= 256 and k % 8 == 0
+            and weight.is_contiguous() and weight.size(1) == k
+            # the tensor-core kernel reads its operands with 16-byte TMA / cp.async copies; a
+            # misaligned view takes the generic pair of calls instead
+            and all(t.data_ptr() % 16 == 0 for t in (b, values, ci, weight)))
 
 
 # ----------------------------------------------------------------------------------------
@@ -219,8 +222,15 @@ class CUDAGraphModulePreviousLayerFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *grads):
-        if ctx.backward_constructor is not None:
-            _replay(ctx.backward_constructor)
+        bc = ctx.backward_constructor
+        if bc is not None and bc.node_count()[0] > 0:
+            # The recorded layer's backward has only RECORDED its kernels (autograd ran it just
+            # before this node): the gradient tensors exist, their contents do not.  Bring the
+            # side streams back to the primary one and run the graph now, before the gradients
+            # travel further up.
+            if len(bc.registeredStreams) > 1:
+                bc.join(bc.registeredStreams[1:], bc.registeredStreams[0])
+            _replay(bc)
         return (None, *grads)
 
 
@@ -282,15 +292,22 @@ class SparseDenseLayer(ModuleToReplay):
                                  fwd_kwargs_2=default_fwd_kwargs())
         if self.mode == "interleaved":
             ctor = forward_constructors[0]
-            if len(ctor.registeredStreams) < 2:
-                ctor.register_new_stream()
+            bctor = backward_constructors[0] if backward_constructors else None
+            for c in (ctor, bctor):
+                if c is not None and len(c.registeredStreams) < 2:
+                    c.register_new_stream()
             xt = x.t().contiguous()
             args = args[:7] + (xt, self.weight_dense)
+            # Without a backward constructor the backward pass runs eagerly (the operators
+            # check for None); with one, both operators record their backward kernels on its
+            # two streams and CUDAGraphModulePreviousLayerFunction replays them.
             outs = self.pair.run(
                 *args,
-                fwd_kwargs_1=default_fwd_kwargs(constructor=ctor, constructor_enabled=True, stream_beg=0,
+                fwd_kwargs_1=default_fwd_kwargs(constructor=ctor, backward_constructor=bctor,
+                                                constructor_enabled=True, stream_beg=0,
                                                 use_tensor_cores=True),
-                fwd_kwargs_2=default_fwd_kwargs(constructor=ctor, constructor_enabled=True, stream_beg=1))
+                fwd_kwargs_2=default_fwd_kwargs(constructor=ctor, backward_constructor=bctor,
+                                                constructor_enabled=True, stream_beg=1))
             ctor.join(ctor.registeredStreams[1:], ctor.registeredStreams[0])
             return outs
         raise ValueError(self.mode)
@@ -308,7 +325,7 @@ class ConstructorEnabledLayer(nn.Module):
         n = self.layer_to_replay.num_parallel_autograd_funcs
         backward_constructors = [TorchCUDAGraphConstructor() for _ in range(n)]
         forward_constructors = [TorchCUDAGraphConstructor() for _ in range(n)]
-        x = CUDAGraphModulePreviousLayerFunction.apply(None, x)
+        x = CUDAGraphModulePreviousLayerFunction.apply(backward_constructors[0], x)
         outs = self.layer_to_replay(x, forward_constructors=forward_constructors,
                                     backward_constructors=backward_constructors)
         outs = outs if isinstance(outs, tuple) else (outs,)

@@ -22,6 +22,7 @@
 #include <torch/library.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <tuple>
 
 #include "iex_b200.h"
@@ -45,6 +46,47 @@ void check_common(std::initializer_list<std::pair<const char*, const at::Tensor*
     if (first == nullptr) first = t;
     TORCH_CHECK(t->device() == first->device(), name, " should be in the same device as the first argument");
   }
+}
+
+// CSR validation on the device (iex_csr_validate): returns 0 or the OR of IEX_CSR_* bits.
+// Synchronises the stream, so it must not run during stream capture.
+int64_t validate_csr_impl(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m,
+                          int64_t k, const at::Tensor* row_indices, bool require_ascending) {
+  c10::cuda::CUDAGuard guard(row_offsets.device());
+  const bool i16 = column_indices.scalar_type() == at::kShort;
+  TORCH_CHECK(i16 || column_indices.scalar_type() == at::kInt, "column_indices must be int16 or int32");
+  TORCH_CHECK(row_offsets.scalar_type() == at::kInt && row_offsets.numel() == m + 1,
+              "row_offsets must be int32 with m + 1 entries");
+  at::Tensor result = at::empty({1}, row_offsets.options());
+  check_status(iex_csr_validate(m, k, column_indices.numel(), row_offsets.data_ptr<int>(),
+                                column_indices.data_ptr(), i16 ? 16 : 32,
+                                row_indices != nullptr ? row_indices->data_ptr<int>() : nullptr,
+                                require_ascending ? 1 : 0, result.data_ptr<int>(), stream_of(row_offsets)),
+               "iex_csr_validate");
+  return result.item<int>();
+}
+
+// With IEX_VALIDATE_CSR=1 in the environment every sparse operator checks its CSR arguments
+// on the device before launching (one extra kernel and a stream synchronisation per call: a
+// debugging aid, off by default and skipped while the stream is being captured).
+bool validation_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("IEX_VALIDATE_CSR");
+    return v != nullptr && v[0] != '\0' && v[0] != '0';
+  }();
+  return on;
+}
+
+void maybe_validate(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t k,
+                    const at::Tensor* row_indices, bool require_ascending) {
+  if (!validation_enabled()) return;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(at::cuda::getCurrentCUDAStream(row_offsets.get_device()).stream(), &cap);
+  if (cap != cudaStreamCaptureStatusNone) return;
+  const int64_t code = validate_csr_impl(row_offsets, column_indices, m, k, row_indices, require_ascending);
+  TORCH_CHECK(code == 0, "malformed CSR argument (IEX_CSR_* bits ", code,
+              "): 1 first offset, 2 last offset, 4 offsets not monotone, 8 column out of range, "
+              "16 columns not ascending, 32 row index out of range");
 }
 
 void check_spmm(const at::Tensor& b, const at::Tensor& row_indices, const at::Tensor& values,
@@ -80,6 +122,7 @@ at::Tensor spmm_f32(const at::Tensor& b, const at::Tensor& row_indices, const at
   TORCH_CHECK(column_indices.scalar_type() == at::kInt, "column_indices must be int32");
   c10::cuda::CUDAGuard guard(b.device());
   const int batch = b.size(0), k = b.size(1), n = b.size(2), nnz = column_indices.size(0);
+  maybe_validate(row_offsets, column_indices, m, k, &row_indices, false);
   at::Tensor out = per_batch_values ? at::zeros({batch, m, n}, b.options()) : at::empty({batch, m, n}, b.options());
   check_status(iex_spmm_f32(m, k, n, nnz, row_indices.data_ptr<int>(), values.data_ptr<float>(),
                             per_batch_values ? nnz : 0, row_offsets.data_ptr<int>(),
@@ -114,6 +157,7 @@ at::Tensor spmm_sputnik_reuse_weight_half(const at::Tensor& b, const at::Tensor&
   TORCH_CHECK(i16 || column_indices.scalar_type() == at::kInt, "column_indices must be int16 or int32");
   c10::cuda::CUDAGuard guard(b.device());
   const int batch = b.size(0), k = b.size(1), n = b.size(2), nnz = column_indices.size(0);
+  maybe_validate(row_offsets, column_indices, m, k, &row_indices, false);
   at::Tensor out = at::empty({batch, m, n}, b.options());
   const int st = i16 ? iex_spmm_f16_i16(m, k, n, nnz, row_indices.data_ptr<int>(), values.data_ptr(),
                                         row_offsets.data_ptr<int>(),
@@ -146,6 +190,7 @@ at::Tensor sddmm_sputnik_atomic_upd_weight(const at::Tensor& a, const at::Tensor
               "row_indices must have m entries and row_offsets m + 1");
   const int nnz = column_indices.size(0);
   c10::cuda::CUDAGuard guard(a.device());
+  maybe_validate(row_offsets, column_indices, m, n, &row_indices, false);
   at::Tensor out = at::empty({nnz}, a.options());
   check_status(iex_sddmm_f32(m, k, n, nnz, row_indices.data_ptr<int>(), row_offsets.data_ptr<int>(),
                              column_indices.data_ptr<int>(), a.data_ptr<float>(), b.data_ptr<float>(),
@@ -206,6 +251,7 @@ at::Tensor spmm_tc_half(const at::Tensor& x, const at::Tensor& row_offsets, cons
                         const at::Tensor& column_indices, int64_t m) {
   const int bits = tc_sparse_checks(x, row_offsets, values, column_indices, m);
   c10::cuda::CUDAGuard guard(x.device());
+  maybe_validate(row_offsets, column_indices, m, x.size(0), nullptr, true);
   at::Tensor out = at::empty({m, x.size(1)}, x.options());
   check_status(iex_spmm_f16_tc(m, x.size(0), x.size(1), column_indices.size(0), row_offsets.data_ptr<int>(),
                                column_indices.data_ptr(), bits, values.data_ptr(), x.data_ptr(),
@@ -224,6 +270,7 @@ std::tuple<at::Tensor, at::Tensor> fused_spmm_linear_half(const at::Tensor& x, c
   check_common({{"x", &x}, {"weight", &weight}});
   TORCH_CHECK(weight.scalar_type() == at::kHalf, "weight must be float16");
   c10::cuda::CUDAGuard guard(x.device());
+  maybe_validate(row_offsets, column_indices, m, x.size(0), nullptr, true);
   const int64_t n = x.size(1), md = weight.size(0);
   at::Tensor out_s = at::empty({m, n}, x.options());
   at::Tensor out_d = at::empty({n, md}, x.options());
@@ -251,6 +298,13 @@ at::Tensor csr_to_dense_half(const at::Tensor& row_offsets, const at::Tensor& va
   return out;
 }
 
+// 0 when the CSR is well formed, else the OR of the IEX_CSR_* bits (include/iex_b200.h)
+int64_t validate_csr(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t k,
+                     bool require_ascending) {
+  check_common({{"row_offsets", &row_offsets}, {"column_indices", &column_indices}});
+  return validate_csr_impl(row_offsets, column_indices, m, k, nullptr, require_ascending);
+}
+
 }  // namespace
 
 TORCH_LIBRARY(iex_ops, m) {
@@ -262,6 +316,7 @@ TORCH_LIBRARY(iex_ops, m) {
   m.def("spmm_tc_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, int m) -> Tensor");
   m.def("fused_spmm_linear_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, int m, Tensor weight) -> (Tensor, Tensor)");
   m.def("csr_to_dense_half(Tensor row_offsets, Tensor values, Tensor column_indices, int m, int k) -> Tensor");
+  m.def("validate_csr(Tensor row_offsets, Tensor column_indices, int m, int k, bool require_ascending) -> int");
 }
 
 // CUDA dispatch key only: a CPU tensor reaches no implementation (there is no CPU path).
@@ -274,4 +329,5 @@ TORCH_LIBRARY_IMPL(iex_ops, CUDA, m) {
   m.impl("spmm_tc_half", &spmm_tc_half);
   m.impl("fused_spmm_linear_half", &fused_spmm_linear_half);
   m.impl("csr_to_dense_half", &csr_to_dense_half);
+  m.impl("validate_csr", &validate_csr);
 }

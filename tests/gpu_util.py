@@ -17,6 +17,33 @@ def close(got, ref, rtol, scale_tol):
     return bool(np.all(np.abs(got - ref) <= bound))
 
 
+def tc_close(got, ref, sum_abs):
+    """Bar for the fp16-in / fp32-accumulate tensor-core kernels, as tight as the arithmetic
+    earns: |got - ref| <= 2^-10 * |ref| (the final rounding to fp16, with a factor two of
+    slack) + 1e-5 * sum_abs, where sum_abs[i, j] = sum_k |a[i, k]| * |b[k, j]| bounds what the
+    order of the fp32 accumulation can change.  A dropped or doubled term (one part in a few
+    thousand of sum_abs at the benchmark sizes) fails it; the task's own bar of 1e-2 relative
+    would not notice one."""
+    ref = np.asarray(ref, dtype=np.float64)
+    got = np.asarray(got, dtype=np.float64)
+    if ref.size == 0:
+        return got.size == 0
+    bound = 2.0 ** -10 * np.abs(ref) + 1e-5 * np.asarray(sum_abs, dtype=np.float64) + 1e-7
+    return bool(np.all(np.abs(got - ref) <= bound))
+
+
+def spmm_ref_and_sum_abs(oracle, a, b, m, bias=None):
+    """fp32 oracle result of A @ b (optionally with bias + ReLU) and |A| @ |b|."""
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, m, bias=bias)[0]
+    sabs = oracle.spmm(a.row_indices, np.abs(a.values), a.row_offsets, a.column_indices, np.abs(b), m)[0]
+    return ref, sabs.astype(np.float64) + (0.0 if bias is None else np.abs(bias)[:, None])
+
+
+def linear_ref_and_sum_abs(x, w):
+    x32, w32 = np.asarray(x, np.float32), np.asarray(w, np.float32)
+    return x32 @ w32.T, np.abs(x32) @ np.abs(w32).T
+
+
 def max_violation(got, ref, rtol, scale_tol):
     ref = np.asarray(ref, dtype=np.float64)
     got = np.asarray(got, dtype=np.float64)

@@ -117,10 +117,10 @@ def test_pair_function_fused_equals_separate(oracle):
                       fwd_kwargs_2=default_fwd_kwargs())
     assert torch.equal(fs, ss)
     assert torch.allclose(fd.float(), sd.float(), rtol=2e-3, atol=2e-3)
-    ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, 384)[0]
-    assert G.close(fs.cpu().numpy(), ref_s, 1e-2, 1e-2)
-    ref_d = x.astype(np.float32).T @ w.astype(np.float32).T
-    assert G.close(fd.cpu().numpy(), ref_d, 1e-2, 1e-2)
+    ref_s, sabs_s = G.spmm_ref_and_sum_abs(oracle, a, x, 384)
+    assert G.tc_close(fs.cpu().numpy(), ref_s, sabs_s)
+    ref_d, sabs_d = G.linear_ref_and_sum_abs(x.T, w)
+    assert G.tc_close(fd.cpu().numpy(), ref_d, sabs_d)
 
 
 def test_pair_function_backward_fp32():
@@ -165,9 +165,10 @@ def test_graph_constructor_two_streams_replay(oracle):
         out_d.zero_()
         ctor.execute_graph()
         ctor.synchronize()
-        ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, 256)[0]
-        assert G.close(out_s.cpu().numpy(), ref_s, 1e-2, 1e-2)
-        assert G.close(out_d.cpu().numpy(), x.astype(np.float32).T @ w.astype(np.float32).T, 1e-2, 1e-2)
+        ref_s, sabs_s = G.spmm_ref_and_sum_abs(oracle, a, x, 256)
+        assert G.tc_close(out_s.cpu().numpy(), ref_s, sabs_s)
+        ref_d, sabs_d = G.linear_ref_and_sum_abs(x.T, w)
+        assert G.tc_close(out_d.cpu().numpy(), ref_d, sabs_d)
     ctor.destroy_graph_exec()
     with pytest.raises(Exception):
         ctor.execute_graph()  # no executable any more
@@ -215,7 +216,53 @@ def test_sparse_dense_layer_modes(oracle):
         else:
             outs[mode] = layer(xd)
         torch.cuda.synchronize()
-    ref_s = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, x, 256)[0]
+    ref_s, sabs_s = G.spmm_ref_and_sum_abs(oracle, a, x, 256)
     for mode, (os_, od) in outs.items():
-        assert G.close(os_.cpu().numpy(), ref_s, 1e-2, 1e-2), mode
+        assert G.tc_close(os_.cpu().numpy(), ref_s, sabs_s), mode
         assert torch.allclose(od.float(), outs["fused"][1].float(), rtol=2e-3, atol=2e-3), mode
+
+
+def test_interleaved_backward_graph_matches_serial():
+    """The backward kernels of the recorded layer go into the backward constructor's graph and
+    are replayed by the layer in front of it; the input gradient must equal the one of the
+    same layer run eagerly ("serial"), and the dense autograd reference within fp16 bounds."""
+    a, w, x = syn.fused_layer_case(7, 256, 512, 64, 256)
+    da = G.DevCSR(a)
+    wd = G.dev(w)
+    info = U.get_transpose_info(256, 512, da.row_indices, da.row_offsets, da.column_indices)
+    g_s = torch.randn(256, 64, device=G.DEV).half()
+    g_d = torch.randn(64, 256, device=G.DEV).half()
+    grads = {}
+    for mode in ("serial", "interleaved"):
+        layer = hr.SparseDenseLayer(da.values, da.row_indices, da.row_offsets, da.column_indices, 256, wd,
+                                    transp_info=info, mode=mode)
+        xd = G.dev(x).requires_grad_(True)
+        net = hr.ConstructorEnabledLayer(layer) if mode == "interleaved" else layer
+        out_s, out_d = net(xd)
+        torch.autograd.backward((out_s, out_d), (g_s, g_d))
+        torch.cuda.synchronize()
+        grads[mode] = xd.grad.clone()
+    assert torch.equal(grads["interleaved"], grads["serial"])
+    dense_a = torch.zeros(256, 512, device=G.DEV)
+    rows = torch.repeat_interleave(torch.arange(256, device=G.DEV), (da.row_offsets[1:] - da.row_offsets[:-1]).long())
+    dense_a[rows, da.column_indices.long()] = da.values.float()
+    ref = dense_a.t() @ g_s.float() + (g_d.float() @ wd.float()).t()
+    assert _scale_close(grads["serial"].float(), ref, 2e-3)
+
+
+def test_misaligned_operands_take_the_unfused_pair():
+    a, w, x = syn.fused_layer_case(8, 128, 256, 64, 128)
+    da = G.DevCSR(a)
+    info = ()
+    xd = G.dev(x)
+    wbuf = torch.empty(128 * 256 + 1, device=G.DEV, dtype=torch.float16)
+    wmis = wbuf[1:].view(128, 256)
+    wmis.copy_(G.dev(w))
+    assert wmis.data_ptr() % 16 != 0
+    args = (xd, da.row_indices, da.values, da.row_offsets, da.column_indices, 128, info, xd.t(), wmis)
+    assert not hr._fusable(args, {})
+    pair = hr.make_kernel_pair_or_triple_autograd_function(MySpMM, MyLinear)
+    out_s, out_d = pair.run(*args, fwd_kwargs_1=default_fwd_kwargs(use_tensor_cores=True),
+                            fwd_kwargs_2=default_fwd_kwargs())
+    ref_d = x.astype(np.float32).T @ w.astype(np.float32).T
+    assert G.close(out_d.cpu().numpy(), ref_d, 2e-3, 2e-3)

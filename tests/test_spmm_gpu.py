@@ -170,7 +170,8 @@ def test_spmm_cfg1_full_size(oracle):
 def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n, idx):
     """Benchmark configuration 3, the whole sweep (36 cases x 2 index widths): fp16 values,
     fp32 accumulate.  The CUDA-core kernel is bit-exact against the oracle and within 1e-2 of
-    the torch CPU path; the tensor-core kernel within 1e-2 of the oracle."""
+    the torch CPU path; the tensor-core kernel within fp16 rounding of the oracle
+    (gpu_util.tc_close, far inside the 1e-2 bar)."""
     a, b = syn.pruned_sweep_case(int(sparsity * 100) + rows, rows, cols, sparsity, n, index_dtype=idx)
     da = G.DevCSR(a)
     got = G.spmm_f16(da, G.dev(b)[None])[0].cpu().numpy()
@@ -183,7 +184,8 @@ def test_spmm_cfg3_sweep(oracle, rows, cols, sparsity, n, idx):
     _lib.call("iex_spmm_f16_tc", rows, cols, n, a.nnz, da.row_offsets.data_ptr(), da.column_indices.data_ptr(),
               16 if idx == np.int16 else 32, da.values.data_ptr(), db.data_ptr(), tc.data_ptr(),
               G.stream_ptr())
-    assert G.close(tc.cpu().numpy(), ref, 1e-2, 1e-2)
+    _ref, sabs = G.spmm_ref_and_sum_abs(oracle, a, b, rows)
+    assert G.tc_close(tc.cpu().numpy(), ref, sabs)
     assert _lib.lib.iex_last_device_status(1) == 0
 
 
