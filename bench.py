@@ -40,6 +40,10 @@ M, N_COLS, K_DIM, DENSITY = 4096, 4096, 64, 0.05
 INSTANCES = 24  # per GPU; ~11 MB of operands each => ~270 MB per step, > L2 (126 MB)
 METRIC = "spmm_sddmm_gflops"
 UNIT = "GFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel on this workload, from
+# one ncu capture per kernel (12 rotating instances; part of an instance is still L2-resident
+# from the kernel before it, hence below the algorithmic bytes)
+NCU_DRAM_BYTES_PER_LAUNCH = {"sddmm_rowtile_kernel": 5.50e6, "spmm_rowgroup_kernel": 7.81e6}
 
 
 def measured_peak_gbs():
@@ -55,9 +59,10 @@ def config_dict(n_gpus: int) -> dict:
     return {
         "workload": "cfg2: fp32 SDDMM 4096x4096 mask @95% sparsity, K=64, then SpMM x V 4096x64",
         "instances_per_gpu": INSTANCES,
-        "l2_policy": "inputs larger than L2: each step streams %d independent instances (~270 MB)" % INSTANCES,
+        "l2_policy": "inputs > L2: a step streams %d instances (~270 MB)" % INSTANCES,
         "index_dtype": "int32",
-        "parallelism": "independent instances per GPU, no collective" if n_gpus > 1 else "single GPU",
+        "sddmm": "value: tensor cores with the mask's plan (pattern-only, prebuilt like row_indices); e2e: reference op, CUDA cores, no plan",
+        "parallelism": "instances per GPU, no collective" if n_gpus > 1 else "single GPU",
     }
 
 
@@ -117,15 +122,56 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def synthetic_module():
+    """The workload generators (pure numpy), loaded by file path so that the CPU reference arm
+    does not import the package, whose import loads the CUDA libraries."""
+    import importlib.util
+    name = "iex_b200_synthetic"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(
+        name, os.path.join(REPO, "intrasm_engine_b200", "synthetic.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def make_instances(rank: int, count: int):
-    from intrasm_engine_b200 import synthetic as syn
+    syn = synthetic_module()
     return [syn.sddmm_chain_case(1000 * rank + i, M, N_COLS, K_DIM, DENSITY) for i in range(count)]
 
 
 def flops_of(inst) -> int:
-    from intrasm_engine_b200 import synthetic as syn
+    syn = synthetic_module()
     mask = inst[0]
     return syn.sddmm_flops(mask.nnz, K_DIM) + syn.spmm_flops(mask.nnz, K_DIM)
+
+
+def emit(line: dict, details: dict | None = None) -> None:
+    """Prints the ONE JSON line (compact separators, floats to 5 significant digits) and puts
+    the long tables next to it: on stderr and, where that folder exists, in
+    gpurun_out/bench_details.json."""
+    def trim(o):
+        if isinstance(o, float):
+            return float("%.5g" % o)
+        if isinstance(o, dict):
+            return {k: trim(v) for k, v in o.items()}
+        if isinstance(o, (list, tuple)):
+            return [trim(v) for v in o]
+        return o
+    if details:
+        text = json.dumps(trim(details))
+        sys.stderr.write("bench details: " + text + "\n")
+        out_dir = os.path.join(REPO, "gpurun_out")
+        if os.path.isdir(out_dir):
+            try:
+                with open(os.path.join(out_dir, "bench_details.json"), "w") as f:
+                    f.write(text + "\n")
+            except OSError:
+                pass
+    print(json.dumps(trim(line), separators=(",", ":")))
+    sys.stdout.flush()
 
 
 # ----------------------------------------------------------------------------------------
@@ -168,17 +214,20 @@ def run_reference(args) -> None:
     warnings.filterwarnings("ignore")
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    sample = 2
-    insts = make_instances(0, sample)
-    fl = sum(flops_of(i) for i in insts)
+    # One step = the whole step's workload (all instances), run INNER times so that the timed
+    # region holds at least a second of CPU work at the default step count.
+    inner = 4
+    insts = make_instances(0, INSTANCES)
+    fl = sum(flops_of(i) for i in insts) * inner
     prepared = [cpu_prepare(inst) for inst in insts]
-    for _ in range(max(args.warmup, 1)):
+    for _ in range(max(min(args.warmup, 3), 1)):
         for pr in prepared:
             cpu_chain_once(pr)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        for pr in prepared:
-            cpu_chain_once(pr)
+        for _r in range(inner):
+            for pr in prepared:
+                cpu_chain_once(pr)
     dt = time.perf_counter() - t0
     value = fl * args.steps / dt / 1e9
     line = {
@@ -187,11 +236,11 @@ def run_reference(args) -> None:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": config_dict(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} of {INSTANCES} instances per step; torch.sparse.sampled_addmm + torch.sparse.mm (CSR, int32 indices), fp32"},
+                         "sample": f"all {INSTANCES} instances of a step, {inner} times per step ({dt:.2f} s timed); torch.sparse.sampled_addmm + torch.sparse.mm (CSR, int32 indices), fp32"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------
@@ -224,18 +273,23 @@ def _bind_to_gpu_numa_node(device_index: int):
 
 
 def run_ours(args) -> None:
-    import intrasm_engine_b200  # noqa: F401  (raises if the CUDA library is missing)
-    from intrasm_engine_b200 import _lib, synthetic as syn
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        # NCCL's INFO lines (communicator size, rings / NVLS) go to stderr, stdout keeps the one
+        # JSON line
+        os.environ["NCCL_DEBUG"] = "INFO"
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    import intrasm_engine_b200  # noqa: F401  (raises if the CUDA library is missing)
+    from intrasm_engine_b200 import _lib, synthetic as syn
+
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
     if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"  # keep NCCL's version banner out of stdout (one JSON line)
         import torch.distributed as dist_mod
         dist = dist_mod
         dist.init_process_group("nccl", device_id=dev)
@@ -259,11 +313,22 @@ def run_ours(args) -> None:
         d.out = torch.empty((M, K_DIM), dtype=torch.float32, device=dev)
         dinst.append(d)
     stream = torch.cuda.current_stream().cuda_stream
+    # Pattern-only plans of the masks for the tensor-core SDDMM, built once like row_indices (the
+    # patterns do not change between steps); the end-to-end region below rebuilds them per step.
+    for d in dinst:
+        d.plan = torch.ops.iex_ops.sddmm_plan(d.ro, d.ci, M, N_COLS)
+    # the kernel the operator layer picks for this shape (tensor cores for a 5 % mask)
+    sddmm_on_tc = bool(_lib.lib.iex_sddmm_f32_prefers_tc(M, K_DIM, N_COLS, dinst[0].nnz, 1))
+    sddmm_kernel = "sddmm_tc_kernel" if sddmm_on_tc else "sddmm_rowtile_kernel"
 
     def sddmm_all():
         for d in dinst:
-            _lib.call("iex_sddmm_f32", M, K_DIM, N_COLS, d.nnz, d.ri.data_ptr(), d.ro.data_ptr(),
-                      d.ci.data_ptr(), d.q.data_ptr(), d.k.data_ptr(), d.scores.data_ptr(), 1, 0, stream)
+            if sddmm_on_tc:
+                _lib.call("iex_sddmm_f32_tc", M, K_DIM, N_COLS, d.nnz, d.plan.data_ptr(),
+                          d.q.data_ptr(), d.k.data_ptr(), d.scores.data_ptr(), 0, stream)
+            else:
+                _lib.call("iex_sddmm_f32", M, K_DIM, N_COLS, d.nnz, d.ri.data_ptr(), d.ro.data_ptr(),
+                          d.ci.data_ptr(), d.q.data_ptr(), d.k.data_ptr(), d.scores.data_ptr(), 1, 0, stream)
 
     def spmm_all():
         for d in dinst:
@@ -353,6 +418,8 @@ def run_ours(args) -> None:
                 ready[b].record(copy_stream)
             cur.wait_event(ready[b])
             q, k, v, ri, ro, ci = [slots[b][o:o + nb].view(dt).view(shape) for o, nb, dt, shape in layout]
+            # the reference's operators as they are: no plan exists for a pattern that has just
+            # arrived from the host, so the SDDMM runs on the CUDA-core kernel here
             scores = ops.sddmm_sputnik_atomic_upd_weight(q[None], k[None], ri, ro, ci)
             out = ops.spmm_sputnik_reuse_weight(v[None], ri, scores, ro, ci, M)
             free[b].record(cur)
@@ -378,7 +445,11 @@ def run_ours(args) -> None:
     e2e_ms = e_start.elapsed_time(e_stop)
     clocks = sampler.stop() if rank == 0 else None
     # the end-to-end path ran the same kernels on the same inputs as the device-resident one
-    e2e_same = all(torch.equal(ho, d.out.cpu()) for ho, d in zip(host_out[:3], dinst[:3]))
+    # (bit for bit when both ran the same SDDMM kernel, else within the fp32 bar)
+    def same(ho, dv):
+        dv = dv.cpu()
+        return torch.equal(ho, dv) or bool(torch.allclose(ho, dv, rtol=1e-4, atol=1e-5 * float(dv.abs().max())))
+    e2e_same = all(same(ho, d.out) for ho, d in zip(host_out[:3], dinst[:3]))
     assert e2e_same, "end-to-end results differ from the device-resident results"
 
     if dist is not None:
@@ -391,9 +462,15 @@ def run_ours(args) -> None:
     else:
         job_flops = float(total_flops)
 
-    ffn = None
+    mean_nnz = sum(d.nnz for d in dinst) / INSTANCES
+    del dinst, host, host_out, slots, outs
+    torch.cuda.empty_cache()
+
+    details = {}
+    ffn = row_split = None
     if not args.no_extras:
-        ffn = ffn_stack_section(dev, rank, world, dist)
+        ffn, details["ffn_stack"] = ffn_stack_section(dev, rank, world, dist)
+        row_split, details["row_split"] = row_split_section(dev, rank, world, dist)
 
     if rank != 0:
         if dist is not None:
@@ -403,29 +480,22 @@ def run_ours(args) -> None:
     value = job_flops * args.steps / (elapsed_ms * 1e-3) / 1e9
     e2e_value = job_flops * e2e_steps / (e2e_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak_gbs()
-    mean_nnz = sum(d.nnz for d in dinst) / INSTANCES
     sddmm_bytes = syn.sddmm_bytes(M, N_COLS, K_DIM, mean_nnz)
     spmm_bytes = syn.spmm_bytes(M, N_COLS, K_DIM, mean_nnz, 4, 4)
     kernels = {
-        "sddmm_rowtile_kernel": {"ms": sddmm_ms, "bytes": sddmm_bytes,
-                                 "gflops": syn.sddmm_flops(mean_nnz, K_DIM) / (sddmm_ms * 1e-3) / 1e9},
-        "spmm_rowgroup_kernel": {"ms": spmm_ms, "bytes": spmm_bytes,
+        sddmm_kernel: {"us": sddmm_ms * 1e3, "bytes": sddmm_bytes,
+                       "gflops": syn.sddmm_flops(mean_nnz, K_DIM) / (sddmm_ms * 1e-3) / 1e9},
+        "spmm_rowgroup_kernel": {"us": spmm_ms * 1e3, "bytes": spmm_bytes,
                                  "gflops": syn.spmm_flops(mean_nnz, K_DIM) / (spmm_ms * 1e-3) / 1e9},
     }
     for kv in kernels.values():
-        kv["achieved_gbs"] = kv["bytes"] / (kv["ms"] * 1e-3) / 1e9
-        kv["frac_of_%s_hbm" % peak_kind] = kv["achieved_gbs"] / peak
-    dom = max(kernels, key=lambda kname: kernels[kname]["ms"])
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised in
-    # profiles/cuda_core_kernels_cfg2.md (12 rotating instances; part of an instance is still
-    # L2-resident from the kernel before it, hence below the algorithmic bytes)
-    ncu_traffic = {"sddmm_rowtile_kernel": 5.50e6, "spmm_rowgroup_kernel": 7.81e6}
-    roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["achieved_gbs"], "peak": peak,
-                "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[dom]["achieved_gbs"] / peak,
-                "traffic": ncu_traffic[dom], "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
-                "us_per_launch": kernels[dom]["ms"] * 1e3,
-                "note": "gather-bound: every nonzero reads a 256-byte dense row through L1/L2 "
-                        "(214 MB per launch vs 8.8 MB of compulsory HBM traffic)"}
+        kv["gbs"] = kv["bytes"] / (kv["us"] * 1e-6) / 1e9
+        kv["frac_hbm"] = kv["gbs"] / peak
+    dom = max(kernels, key=lambda kname: kernels[kname]["us"])
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak,
+                "peak_kind": peak_kind, "unit": "GB/s", "frac": kernels[dom]["gbs"] / peak,
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(dom), "algorithmic_bytes_per_launch": kernels[dom]["bytes"],
+                "us_per_launch": kernels[dom]["us"]}
 
     cpu = None
     if world == 1:
@@ -442,15 +512,12 @@ def run_ours(args) -> None:
                 all_times.extend(times)
         med = statistics.median(all_times)
         cpu = {"value": flops_of(insts[0]) / med / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": "%d of %d instances, median of %d runs (about 3 s of CPU work); torch.sparse.sampled_addmm + torch.sparse.mm fp32, int32 CSR" % (n_cpu, INSTANCES, len(all_times)),
-               "ms_per_instance": med * 1e3}
+               "sample": "%d of %d instances, median of %d runs (~3 s); torch.sparse.sampled_addmm + sparse.mm fp32" % (n_cpu, INSTANCES, len(all_times))}
 
     fused_layer = other = None
     if world == 1 and not args.no_extras:
-        del dinst, host, host_out, slots
-        torch.cuda.empty_cache()
-        fused_layer = fused_layer_section(dev)
-        other = other_configs_section(dev)
+        other, details["other_configs"] = other_configs_section(dev)
+        fused_layer, details["fused_layer"] = fused_layer_section(dev)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -460,9 +527,9 @@ def run_ours(args) -> None:
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "steps": e2e_steps},
         "gpu_launches": args.steps * INSTANCES * 2, "clocks": clocks, "kernels": kernels,
-        "fused_layer": fused_layer, "other_configs": other, "ffn_stack": ffn,
+        "other_configs": other, "row_split": row_split, "fused_layer": fused_layer, "ffn_stack": ffn,
     }
-    print(json.dumps(line))
+    emit(line, details)
     if dist is not None:
         dist.destroy_process_group()
 
@@ -471,7 +538,7 @@ def run_ours(args) -> None:
 # Extra section: benchmark configuration 4, the fused sparse || dense layer (1 GPU)
 # ----------------------------------------------------------------------------------------
 
-def fused_layer_section(dev, iters: int = 20, warmup: int = 5) -> dict:
+def fused_layer_section(dev, iters: int = 20, warmup: int = 5):
     """LLaMA-7B-shaped layer, fp16, 64 tokens: W_up 11008x4096 CSR @50 % and W_qkv 12288x4096
     dense on the same X 4096x64.  Times (CUDA events, two weight copies rotating so that
     every launch streams its weights from HBM, 2 x 195 MB > L2): the dense branch, the
@@ -540,7 +607,11 @@ def fused_layer_section(dev, iters: int = 20, warmup: int = 5) -> dict:
             torch.cuda.synchronize()
         return e0.elapsed_time(e1) / iters * 1e3
 
+    def library_dense(c):  # the library GEMM on the same operands, for comparison only
+        torch.mm(c["xt"], c["w"].t(), out=c["od"])
+
     us = {
+        "dense_library_us": timeit(lambda i: library_dense(copies[i])),
         "dense_us": timeit(lambda i: dense(copies[i])),
         "sparse_us": timeit(lambda i: sparse(copies[i])),
         "serial_us": timeit(lambda i: serial(copies[i])),
@@ -568,7 +639,15 @@ def fused_layer_section(dev, iters: int = 20, warmup: int = 5) -> dict:
         "fused_gflops": fl / us["fused_us"] / 1e3,
         "status": _lib.lib.iex_last_device_status(1),
     })
-    return out
+    compact = {"cfg": "cfg4 W_up 11008x4096 CSR@50% || W_qkv 12288x4096, 64 tok, fp16",
+               "dense_us": us["dense_us"], "dense_library_us": us["dense_library_us"],
+               "sparse_us": us["sparse_us"], "serial_us": us["serial_us"],
+               "interleaved_graph_us": us["interleaved_graph_us"], "fused_us": us["fused_us"],
+               "fused_vs_serial": out["fused_vs_serial"],
+               "fused_vs_slower_branch_roofline": out["fused_vs_slower_branch_roofline"],
+               "fused_vs_shared_hbm_floor": out["fused_vs_shared_hbm_floor"],
+               "frac_hbm_fused": out["frac_hbm"]["fused"], "status": out["status"]}
+    return compact, out
 
 
 # ----------------------------------------------------------------------------------------
@@ -606,7 +685,7 @@ def _cold_launch_us(fn, reps=9):
     return statistics.median(times)
 
 
-def other_configs_section(dev) -> dict:
+def other_configs_section(dev):
     """Configurations 1 and 3 (small SpMMs: cold single launch and warm rotation over > L2)."""
     from intrasm_engine_b200 import _lib, synthetic as syn
     st = torch.cuda.current_stream().cuda_stream
@@ -677,78 +756,78 @@ def other_configs_section(dev) -> dict:
                         "mean_time_vs_best": round(sum(regret) / len(regret), 3),
                         "worst_time_vs_best": round(max(regret), 3)}
     out["cfg3_spmm_fp16_sweep"] = sweep
-    return out
+    c1d = out["cfg1_spmm_fp32"]
+    fr = [v["frac_hbm_best"] for key, v in sweep.items() if key != "summary"]
+    compact = {"cfg1_us": c1d["us_per_launch_rotating"], "cfg1_cold_us": c1d["us_cold_single_launch"],
+               "cfg1_frac_hbm": c1d["frac_hbm"],
+               "cfg3": dict(sweep["summary"], frac_hbm_min=min(fr), frac_hbm_max=max(fr))}
+    return compact, out
 
 
-def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dict:
-    """Configuration 5: 32 ReLU-sparse FFN down projections, fp16, 256 tokens.  The activation
-    CSR (256x11008, 90 % zeros) is replicated; W_down (11008x4096) is sharded by columns over
-    the ranks; each layer gathers the [256, 4096/G] outputs on every rank, either with an NCCL
+def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32):
+    """Configuration 5: 32 ReLU-sparse FFN down projections, fp16, 256 tokens, through the
+    product module (intrasm_engine_b200.pytorch.ffn.ReluSparseDownProj).  The activation CSR
+    (256x11008, 90 % zeros) is replicated; W_down (11008x4096) is sharded by columns over the
+    ranks; each layer gathers the [256, 4096/G] outputs on every rank, either with an NCCL
     all-gather or by the linear kernel's own stores into the peers' buffers followed by a
-    barrier kernel (both are timed; the faster one is reported).  The local product
-    expands the activation CSR to a dense [256, 11008] tile operand and runs the tensor-core
-    linear on this rank's slab (stored [4096/G, 11008], K-major)."""
+    barrier kernel (both are timed; the faster one is reported).  Before the timing every rank
+    checks one layer of each gather method against the single-GPU computation of all G slabs
+    (same kernels, same split-K part order: bit-identical) -- ``parity_ok``."""
     from intrasm_engine_b200 import _lib, synthetic as syn
-    from intrasm_engine_b200.pytorch.distributed import all_gather_columns
+    from intrasm_engine_b200.pytorch.ffn import ReluSparseDownProj
     tokens, k, n = 256, 11008, 4096
     n_local = n // world
-    st = torch.cuda.current_stream().cuda_stream
     slabs = 4  # distinct weight slabs rotating (4 x 90 MB / G), so weights stream from HBM
-    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-    w = [(torch.randn((n_local, k), generator=gen, device=dev) * 0.02).half() for _ in range(slabs)]
+    # every rank draws the same full weights (same seed) and keeps its own column slab
+    gen = torch.Generator(device=dev).manual_seed(1234)
+    w_full = [(torch.randn((n, k), generator=gen, device=dev) * 0.02).half() for _ in range(slabs)]
+    w = [wf[rank * n_local:(rank + 1) * n_local].contiguous() for wf in w_full]
     acts = []
     for layer in range(4):
         a, _ = syn.relu_ffn_layer_case(0, layer, tokens, k, n, with_weight=False)
         acts.append((torch.as_tensor(a.values).to(dev), torch.as_tensor(a.row_offsets).to(dev),
                      torch.as_tensor(a.column_indices).to(dev), a.nnz))
-    tiles = (n_local + 127) // 128
-    # With few 128-row tiles per rank a tile-per-CTA schedule leaves most SMs idle and every
-    # CTA is bound by its own TMA pipeline (~110 GB/s); split-K spreads a tile's K range over
-    # ~128 / tiles CTAs (measured optimum: 32 tiles -> 4 parts, 16 -> 8, <= 8 -> 16).
-    parts = max(1, min(16, 128 // tiles))
-    need = _lib.lib.iex_tc_workspace_bytes(0, 1, n_local, parts, tokens)
-    ws = torch.empty(max(need, 256), dtype=torch.uint8, device=dev)
-    out_local = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)
-    dense = torch.empty((tokens, k), dtype=torch.float16, device=dev)
-
-    peer = None
+    mods = {"none": ReluSparseDownProj(tokens, k, n, rank, world, dev, gather="none")}
     if world > 1:
-        from intrasm_engine_b200.pytorch.distributed import PeerGather
-        peer = PeerGather(tokens, n, rank, world, dev)
+        mods["nccl"] = ReluSparseDownProj(tokens, k, n, rank, world, dev, gather="nccl")
+        mods["peer"] = ReluSparseDownProj(tokens, k, n, rank, world, dev, gather="peer")
+    parts = mods["none"].parts
 
-    def layer_fn(i, gather=True):
-        vals, ro, ci, _nnz = acts[i % 4]
-        _lib.call("iex_csr_to_dense_f16", tokens, k, ro.data_ptr(), ci.data_ptr(), 32, vals.data_ptr(),
-                  dense.data_ptr(), st)
-        if gather == "peer":
-            # the linear's own threads store the slab into every rank's result buffer; one
-            # small barrier kernel per layer orders the stores before the next use
-            peer.linear(i % 2, dense, w[i % slabs], parts, ws, st)
-            peer.barrier(st)
-            return peer.result(i % 2)
-        _lib.call("iex_linear_f16_splitk", tokens, k, n_local, dense.data_ptr(), w[i % slabs].data_ptr(),
-                  out_local.data_ptr(), parts, ws.data_ptr(), ws.numel(), st)
-        return all_gather_columns(out_local) if (gather and world > 1) else out_local
+    # ---- parity: gathered result == the G slabs computed one after the other on this GPU
+    single = ReluSparseDownProj(tokens, k, n_local, 0, 1, dev, gather="none")
+    vals, ro, ci, _nnz = acts[1]
+    expect = torch.cat([single(vals, ro, ci, w_full[1][r * n_local:(r + 1) * n_local].contiguous()).clone()
+                        for r in range(world)], dim=1)
+    parity = {}
+    for g, mod in mods.items():
+        got = mod(vals, ro, ci, w[1])
+        torch.cuda.synchronize()
+        parity[g] = bool(torch.equal(got, expect if g != "none" else expect[:, rank * n_local:(rank + 1) * n_local]))
+    # and the product itself against the library GEMM on the expanded activations
+    ref = (mods["none"].dense_act.float() @ w_full[1].float().t())
+    rel = float((expect.float() - ref).abs().max() / ref.abs().max())
+    parity_ok = all(parity.values()) and rel < 2e-3
+    del single, expect, ref, w_full
+    torch.cuda.empty_cache()
 
-    def stack(gather=True):
+    def stack(g, st):
+        mod = mods[g]
         for i in range(layers):
-            layer_fn(i, gather)
+            vals, ro, ci, _nnz = acts[i % 4]
+            mod(vals, ro, ci, w[i % slabs], stream=st)
 
     # The stack is launch-bound when driven from Python (3-4 launches per layer), so each
     # variant is captured once into a CUDA graph (kernels and NCCL all-gathers) and replayed.
-    def timed(gather) -> float:
+    def timed(g) -> float:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            nonlocal st
-            st_saved, st = st, side.cuda_stream
             for _ in range(2):
-                stack(gather)
+                stack(g, side.cuda_stream)
             side.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                stack(gather)
-            st = st_saved
+                stack(g, side.cuda_stream)
         torch.cuda.current_stream().wait_stream(side)
         if dist is not None:
             dist.barrier()
@@ -764,25 +843,167 @@ def ffn_stack_section(dev, rank: int, world: int, dist, layers: int = 32) -> dic
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / reps
 
-    ms_nccl = timed(True)
-    ms_nogather = timed(False) if world > 1 else ms_nccl
-    ms_peer = timed("peer") if world > 1 else ms_nccl
+    # the library GEMM on the same dense operand (one layer, no expansion, no gather)
+    dense = mods["none"].dense_act
+    outl = torch.empty((tokens, n_local), dtype=torch.float16, device=dev)
+    lib_us = _time_us(lambda i: torch.mm(dense, w[i % slabs].t(), out=outl), iters=32, warmup=8)
+    own_us = _time_us(lambda i: _lib.call("iex_linear_f16_splitk", tokens, k, n_local, dense.data_ptr(),
+                                          w[i % slabs].data_ptr(), outl.data_ptr(), parts,
+                                          mods["none"].workspace.data_ptr(), mods["none"].workspace.numel(),
+                                          torch.cuda.current_stream().cuda_stream), iters=32, warmup=8)
+
+    ms_nogather = timed("none")
+    ms_nccl = timed("nccl") if world > 1 else ms_nogather
+    ms_peer = timed("peer") if world > 1 else ms_nogather
+    flags = torch.tensor([ms_nccl, ms_nogather, ms_peer, 0.0 if parity_ok else 1.0], device=dev, dtype=torch.float64)
     if dist is not None:
-        tt = torch.tensor([ms_nccl, ms_nogather, ms_peer], device=dev, dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms_nccl, ms_nogather, ms_peer = float(tt[0]), float(tt[1]), float(tt[2])
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    ms_nccl, ms_nogather, ms_peer = float(flags[0]), float(flags[1]), float(flags[2])
+    parity_ok = float(flags[3]) == 0.0
     ms = min(ms_nccl, ms_peer)
     status = _lib.lib.iex_last_device_status(0)
     nnz = acts[0][3]
     peak, _ = measured_peak_gbs()
     by = nnz * 6 + 4 * (tokens + 1) + 4 * tokens + k * n_local * 2 + tokens * n_local * 2
-    return {"workload": "cfg5: 32 x (act 256x11008 CSR@90% x W_down 11008x4096 fp16), W_down column-sharded",
+    full = {"workload": "cfg5: 32 x (act 256x11008 CSR@90% x W_down 11008x4096 fp16), W_down column-sharded",
             "layers": layers, "gpus": world, "split_k_parts": parts, "us_per_layer": ms / layers * 1e3,
             "us_per_layer_peer_store_gather": ms_peer / layers * 1e3,
             "us_per_layer_nccl_allgather": ms_nccl / layers * 1e3,
             "us_per_layer_without_allgather": ms_nogather / layers * 1e3, "device_status": status,
+            "parity_ok": parity_ok, "parity_by_gather": parity, "rel_err_vs_library_gemm": rel,
+            "linear_us": own_us, "linear_library_us": lib_us,
             "useful_gflops": 2.0 * nnz * n / (ms / layers * 1e-3) / 1e9,
             "bytes_per_layer_per_gpu": by, "frac_hbm_per_gpu": by / (ms_nogather / layers * 1e-3) / 1e9 / peak}
+    compact = {"cfg": "cfg5 32 x (act 256x11008 CSR@90% x W_down 11008x4096), col-sharded", "gpus": world,
+               "us_per_layer": full["us_per_layer"], "peer_us": full["us_per_layer_peer_store_gather"],
+               "nccl_us": full["us_per_layer_nccl_allgather"], "nogather_us": full["us_per_layer_without_allgather"],
+               "linear_us": own_us, "linear_library_us": lib_us, "frac_hbm_per_gpu": full["frac_hbm_per_gpu"],
+               "parity_ok": parity_ok, "status": status}
+    for mod in mods.values():
+        mod.peer = None
+    return compact, full
+
+
+def row_split_section(dev, rank: int, world: int, dist):
+    """ONE matrix cut by rows over the ranks (no collective on the data path): the
+    configuration-4 layer -- W_up's rows in nnz-balanced contiguous ranges, W_qkv's rows evenly,
+    X replicated -- and one configuration-2 instance (mask rows nnz-balanced, Q rows with them,
+    K and V replicated).  Every rank times its own share; the job's time is the slowest rank's.
+    Each rank also computes the whole problem once and compares its rows of the result."""
+    from intrasm_engine_b200 import _lib, synthetic as syn
+    from intrasm_engine_b200.pytorch.utils import nnz_balanced_row_split
+    st = torch.cuda.current_stream().cuda_stream
+
+    def up(z):
+        return torch.as_tensor(np.ascontiguousarray(z)).to(dev)
+
+    def reduce_max(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    # ---- configuration 4, fused launch on this rank's rows
+    MS, MD, K, N = 11008, 12288, 4096, 64
+    a, wq, x = syn.fused_layer_case(0, MS, K, N, MD)
+    ro_full = torch.as_tensor(a.row_offsets)
+    r0, r1 = nnz_balanced_row_split(ro_full, world)[rank]
+    d0, d1 = rank * MD // world // 8 * 8, ((rank + 1) * MD // world // 8 * 8 if rank + 1 < world else MD)
+    p0, p1 = int(a.row_offsets[r0]), int(a.row_offsets[r1])
+    ro = up(a.row_offsets[r0:r1 + 1] - a.row_offsets[r0])
+    ci, va = up(a.column_indices[p0:p1]), up(a.values[p0:p1])
+    w_loc, xd = up(wq[d0:d1]), up(x)
+    # two copies of the local weights rotate so that launches stream from HBM when the share is
+    # smaller than L2
+    sets = []
+    for _ in range(2 if world < 4 else 6):
+        sets.append((ro, ci.clone(), va.clone(), w_loc.clone(),
+                     torch.empty((r1 - r0, N), dtype=torch.float16, device=dev),
+                     torch.empty((N, d1 - d0), dtype=torch.float16, device=dev)))
+
+    def fused(i):
+        ro_, ci_, va_, w_, os_, od_ = sets[i % len(sets)]
+        _lib.call("iex_fused_spmm_linear_f16", r1 - r0, d1 - d0, K, N, p1 - p0, ro_.data_ptr(), ci_.data_ptr(), 16,
+                  va_.data_ptr(), w_.data_ptr(), xd.data_ptr(), os_.data_ptr(), od_.data_ptr(), 1, st)
+
+    if dist is not None:
+        dist.barrier()
+    fused_us = _time_us(fused, iters=20, warmup=5)
+    # parity: the whole layer on this GPU, this rank's rows of it
+    full_s = torch.empty((MS, N), dtype=torch.float16, device=dev)
+    full_d = torch.empty((N, MD), dtype=torch.float16, device=dev)
+    fro, fci, fva, fw = up(a.row_offsets), up(a.column_indices), up(a.values), up(wq)
+    _lib.call("iex_fused_spmm_linear_f16", MS, MD, K, N, a.nnz, fro.data_ptr(), fci.data_ptr(), 16, fva.data_ptr(),
+              fw.data_ptr(), xd.data_ptr(), full_s.data_ptr(), full_d.data_ptr(), 1, st)
+    fused(0)
+    torch.cuda.synchronize()
+    ok4 = bool(torch.equal(sets[0][4], full_s[r0:r1]) and
+               torch.allclose(sets[0][5].float(), full_d[:, d0:d1].float(), rtol=2e-3, atol=2e-3))
+    nnz_share = (p1 - p0) / max(a.nnz, 1)
+    del sets, full_s, full_d, fro, fci, fva, fw, w_loc
+    torch.cuda.empty_cache()
+
+    # ---- configuration 2, SDDMM -> SpMM on this rank's rows of one instance
+    mask, q, kk, v = syn.sddmm_chain_case(77, M, N_COLS, K_DIM, DENSITY)
+    b0, b1 = nnz_balanced_row_split(torch.as_tensor(mask.row_offsets), world)[rank]
+    q0, q1 = int(mask.row_offsets[b0]), int(mask.row_offsets[b1])
+    mrows = b1 - b0
+    lro = up(mask.row_offsets[b0:b1 + 1] - mask.row_offsets[b0])
+    lri = up(syn.swizzle_rows(mask.row_offsets[b0:b1 + 1] - mask.row_offsets[b0]))
+    copies = min(96, 12 * world)  # 12 x 11 MB / world per copy set: rotate over more than L2
+    runs = [(lro, lri, up(mask.column_indices[q0:q1]), up(q[b0:b1]), up(kk), up(v),
+             torch.empty(q1 - q0, device=dev), torch.empty((mrows, K_DIM), device=dev)) for _ in range(copies)]
+    on_tc = bool(_lib.lib.iex_sddmm_f32_prefers_tc(mrows, K_DIM, N_COLS, q1 - q0, 1))
+    lplan = torch.ops.iex_ops.sddmm_plan(lro, runs[0][2], mrows, N_COLS) if on_tc else None
+
+    def chain(i):
+        ro_, ri_, ci_, q_, k_, v_, sc_, o_ = runs[i % copies]
+        if on_tc:
+            _lib.call("iex_sddmm_f32_tc", mrows, K_DIM, N_COLS, q1 - q0, lplan.data_ptr(), q_.data_ptr(),
+                      k_.data_ptr(), sc_.data_ptr(), 0, st)
+        else:
+            _lib.call("iex_sddmm_f32", mrows, K_DIM, N_COLS, q1 - q0, ri_.data_ptr(), ro_.data_ptr(), ci_.data_ptr(),
+                      q_.data_ptr(), k_.data_ptr(), sc_.data_ptr(), 1, 0, st)
+        _lib.call("iex_spmm_f32", mrows, N_COLS, K_DIM, q1 - q0, ri_.data_ptr(), sc_.data_ptr(), 0, ro_.data_ptr(),
+                  ci_.data_ptr(), v_.data_ptr(), None, o_.data_ptr(), 1, 0, st)
+
+    if dist is not None:
+        dist.barrier()
+    chain_us = _time_us(chain, iters=48, warmup=12)
+    # parity: the whole instance with the same kernels, this rank's rows
+    fro, fri, fci = up(mask.row_offsets), up(mask.row_indices), up(mask.column_indices)
+    fq, fsc, fo = up(q), torch.empty(mask.nnz, device=dev), torch.empty((M, K_DIM), device=dev)
+    k_, v_ = runs[0][4], runs[0][5]
+    if on_tc:
+        fplan = torch.ops.iex_ops.sddmm_plan(fro, fci, M, N_COLS)
+        _lib.call("iex_sddmm_f32_tc", M, K_DIM, N_COLS, mask.nnz, fplan.data_ptr(), fq.data_ptr(),
+                  k_.data_ptr(), fsc.data_ptr(), 0, st)
+    else:
+        _lib.call("iex_sddmm_f32", M, K_DIM, N_COLS, mask.nnz, fri.data_ptr(), fro.data_ptr(), fci.data_ptr(),
+                  fq.data_ptr(), k_.data_ptr(), fsc.data_ptr(), 1, 0, st)
+    _lib.call("iex_spmm_f32", M, N_COLS, K_DIM, mask.nnz, fri.data_ptr(), fsc.data_ptr(), 0, fro.data_ptr(),
+              fci.data_ptr(), v_.data_ptr(), None, fo.data_ptr(), 1, 0, st)
+    chain(0)
+    torch.cuda.synchronize()
+    sc_l, o_l = runs[0][6], runs[0][7]
+    ok2 = bool(torch.allclose(sc_l, fsc[q0:q1], rtol=1e-5, atol=1e-5 * float(fsc.abs().max())) and
+               torch.allclose(o_l, fo[b0:b1], rtol=1e-4, atol=1e-5 * float(fo.abs().max())))
+    flags = torch.tensor([0.0 if (ok4 and ok2) else 1.0], device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+    fused_max, chain_max = reduce_max(fused_us), reduce_max(chain_us)
+    fl4 = syn.spmm_flops(a.nnz, N) + syn.gemm_flops(MD, N, K)
+    fl2 = syn.sddmm_flops(mask.nnz, K_DIM) + syn.spmm_flops(mask.nnz, K_DIM)
+    full = {"gpus": world, "cfg4_fused_us_this_rank": fused_us, "cfg4_fused_us_max_over_ranks": fused_max,
+            "cfg4_nnz_share_this_rank": nnz_share, "cfg4_gflops": fl4 / fused_max / 1e3,
+            "cfg2_chain_us_this_rank": chain_us, "cfg2_chain_us_max_over_ranks": chain_max,
+            "cfg2_gflops": fl2 / chain_max / 1e3, "cfg2_sddmm_on_tensor_cores": on_tc,
+            "parity_ok": float(flags[0]) == 0.0, "status": _lib.lib.iex_last_device_status(0)}
+    compact = {"cfg": "ONE cfg4 layer / ONE cfg2 instance cut by rows over the GPUs, no collective",
+               "gpus": world, "cfg4_fused_us": fused_max, "cfg4_gflops": full["cfg4_gflops"],
+               "cfg2_chain_us": chain_max, "cfg2_gflops": full["cfg2_gflops"], "parity_ok": full["parity_ok"]}
+    return compact, full
 
 
 def profile_kernel(which: str) -> None:
@@ -797,7 +1018,7 @@ def profile_kernel(which: str) -> None:
     def up(z):
         return torch.as_tensor(np.ascontiguousarray(z)).to(dev)
 
-    if which in ("sddmm", "spmm"):
+    if which in ("sddmm", "spmm", "sddmm_tc"):
         runs = []
         for i in range(12):  # 12 x 11 MB > L2
             mask, q, k, v = syn.sddmm_chain_case(i, M, N_COLS, K_DIM, DENSITY)
@@ -808,6 +1029,10 @@ def profile_kernel(which: str) -> None:
                 if which == "sddmm":
                     _lib.call("iex_sddmm_f32", M, K_DIM, N_COLS, nnz, ri.data_ptr(), ro.data_ptr(), ci.data_ptr(),
                               q.data_ptr(), k.data_ptr(), sc.data_ptr(), 1, 0, st)
+                elif which == "sddmm_tc":
+                    plan = torch.ops.iex_ops.sddmm_plan(ro, ci, M, N_COLS)
+                    _lib.call("iex_sddmm_f32_tc", M, K_DIM, N_COLS, nnz, plan.data_ptr(),
+                              q.data_ptr(), k.data_ptr(), sc.data_ptr(), 0, st)
                 else:
                     _lib.call("iex_spmm_f32", M, N_COLS, K_DIM, nnz, ri.data_ptr(), sc.data_ptr(), 0, ro.data_ptr(),
                               ci.data_ptr(), v.data_ptr(), None, o.data_ptr(), 1, 0, st)
@@ -842,10 +1067,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-kernel", default=None,
-                    choices=["sddmm", "spmm", "linear", "spmm_tc", "fused"],
+                    choices=["sddmm", "sddmm_tc", "spmm", "linear", "spmm_tc", "fused"],
                     help="run a few launches of one kernel on its benchmark workload and exit")
     ap.add_argument("--no-extras", action="store_true",
-                    help="skip the fused-layer section (used for profiler captures)")
+                    help="skip the sections beside the primary workload (used for profiler captures)")
     args = ap.parse_args()
     if args.profile_kernel:
         profile_kernel(args.profile_kernel)

@@ -36,6 +36,7 @@ extern "C" {
 #define IEX_ERR_TOO_LARGE (-3)    /* exceeds a fixed-size resource named in the comment */
 #define IEX_ERR_DRIVER (-4)       /* a driver entry point (tensor-map encode) failed   */
 #define IEX_ERR_TIMEOUT (-5)      /* a bounded device-side wait gave up (status word)  */
+#define IEX_ERR_BAD_CSR (-6)      /* malformed CSR argument (see iex_csr_validate)        */
 
 /* Human-readable text for any return value above (static storage, never NULL). */
 IEX_API const char* iex_error_string(int status);
@@ -94,6 +95,35 @@ IEX_API int iex_sddmm_f32(int m, int k, int n, int nnz, const int32_t* row_indic
                   const int32_t* row_offsets, const int32_t* column_indices,
                   const float* lhs, const float* rhs, float* out, int batch,
                   int accumulate, void* stream);
+
+/* SDDMM on tensor cores (tcgen05.mma.kind::tf32 into TMEM), fp32 in and out; same result
+ * contract as iex_sddmm_f32 with batch = 1 (replaces my_sputnik::CudaSddmm2,
+ * extensions.h:19-26, :31).  The dense product of a 128-row band of lhs with 128 rows of
+ * rhs is formed per tile -- each value split into a TF32 head and tail, three products per
+ * tile, error below 2^-19 of sum |lhs||rhs| -- and only the stored positions are written,
+ * out[] in storage order as always.
+ *
+ * Which positions a tile holds comes from a PLAN, a pattern-only argument like the
+ * reference's row_indices (computed once per sparsity pattern, reused by every call on it):
+ * the stored positions regrouped by 128 x 128 tile.
+ *   iex_sddmm_plan_bytes   size of a plan for an m x n pattern with nnz stored positions
+ *   iex_sddmm_plan_build   fills `plan` (device memory, 16-byte aligned, caller-owned) from
+ *                          row_offsets / column_indices: a memset and three small kernels on
+ *                          `stream`.  Column indices need not ascend; an index outside [0, n)
+ *                          is left out of the plan (its out[] position is not written).
+ *   iex_sddmm_f32_tc       the product; `plan` must have been built for the same m, n, nnz.
+ * Limits: k = 32 or 64, lhs / rhs 16-byte aligned (else IEX_ERR_UNSUPPORTED).
+ * iex_sddmm_f32_tc_supported tells whether a shape is inside the limits;
+ * iex_sddmm_f32_prefers_tc whether this kernel is expected to beat the CUDA-core one
+ * (its time follows m * n, the CUDA-core kernel's follows nnz). */
+IEX_API size_t iex_sddmm_plan_bytes(int m, int n, int nnz);
+IEX_API int iex_sddmm_plan_build(int m, int n, int nnz, const int32_t* row_offsets,
+                                 const int32_t* column_indices, void* plan, size_t plan_bytes,
+                                 void* stream);
+IEX_API int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, const float* lhs,
+                             const float* rhs, float* out, int accumulate, void* stream);
+IEX_API int iex_sddmm_f32_tc_supported(int m, int k, int n, int batch);
+IEX_API int iex_sddmm_f32_prefers_tc(int m, int k, int n, int nnz, int batch);
 
 /* ------------------------------------------------------------------------------------
  * Tensor-core (tcgen05 / TMEM / TMA) entry points, fp16 storage, fp32 accumulate.
@@ -268,6 +298,10 @@ IEX_API int iex_csr_validate(int m, int k, int nnz, const int32_t* row_offsets,
                              const void* column_indices, int index_bits,
                              const int32_t* row_indices, int require_ascending,
                              int32_t* result, void* stream);
+
+/* 1 while `stream` is being captured into a CUDA graph, else 0.  Callers that want to
+ * synchronise or read a result back (the CSR check above) ask this first. */
+IEX_API int iex_stream_is_capturing(void* stream);
 
 /* Last device-side failure recorded by any kernel of this library (0 = none).
  * Synchronises the device.  clear != 0 resets the word. */

@@ -32,6 +32,14 @@ SIGNATURES = {
     # m k n nnz row_indices row_offsets cols lhs rhs out batch accumulate stream
     "iex_sddmm_f32": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                               c_ptr, c_int, c_int, c_ptr]),
+    # m n nnz
+    "iex_sddmm_plan_bytes": (c_size, [c_int, c_int, c_int]),
+    # m n nnz row_offsets cols plan plan_bytes stream
+    "iex_sddmm_plan_build": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
+    # m k n nnz plan lhs rhs out accumulate stream
+    "iex_sddmm_f32_tc": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
+    "iex_sddmm_f32_tc_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "iex_sddmm_f32_prefers_tc": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     # tokens in_features out_features input weight out stream
     "iex_linear_f16": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr]),
     # m k n nnz row_offsets cols index_bits values dense out stream
@@ -70,6 +78,7 @@ SIGNATURES = {
     "iex_csr_to_dense_f16": (c_int, [c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_ptr]),
     # m k nnz row_offsets cols index_bits row_indices require_ascending result stream
     "iex_csr_validate": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_int, c_ptr, c_ptr]),
+    "iex_stream_is_capturing": (c_int, [c_ptr]),
     "iex_last_device_status": (c_int, [c_int]),
     # graph constructor (opaque handle first)
     "iex_graph_create": (c_ptr, []),

@@ -36,6 +36,8 @@ sddmm_rowtile_kernel(int m, int k, int n, const int* __restrict__ row_indices,
   const unsigned submask = (W == 32) ? 0xffffffffu : (((1u << (W & 31)) - 1u) << (sub * W));
   const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int slot = warp * (32 / W) + sub;
+  grid_dependency_wait();  // the kernel before this one may have written what is read below
+  grid_launch_dependents();
   if (slot >= m) return;
 
   const int r = __ldg(row_indices + slot);
@@ -125,9 +127,8 @@ int launch(int m, int k, int n, int nnz, const int* ri, const int* ro, const int
   int split = static_cast<int>((avg + 2 * W - 1) / (2 * W));
   split = split < 1 ? 1 : (split > 64 ? 64 : split);
   dim3 grid((m + kRowsPerBlock - 1) / kRowsPerBlock, split, 1);
-  sddmm_rowtile_kernel<W, NV><<<grid, 128, 0, stream>>>(m, k, n, ri, ro, cols, lhs, rhs, out,
-                                                        batch, accumulate);
-  return launch_status();
+  return launch_overlapped(sddmm_rowtile_kernel<W, NV>, grid, dim3(128), 0, stream, m, k, n, ri, ro, cols, lhs, rhs,
+                           out, batch, accumulate);
 }
 
 }  // namespace

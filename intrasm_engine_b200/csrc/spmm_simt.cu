@@ -159,6 +159,8 @@ spmm_rowgroup_kernel(int m, int k, int n, int nnz, const int* __restrict__ row_i
       (LPR == 32) ? 0xffffffffu : (((1u << (LPR & 31)) - 1u) << (sub * LPR));
   const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int slot = warp * (32 / LPR) + sub;
+  grid_dependency_wait();  // the kernel before this one may have written what is read below
+  grid_launch_dependents();
   if (slot >= m) return;  // the whole row group leaves together
 
   const int r = __ldg(row_indices + slot);
@@ -275,10 +277,8 @@ int launch(int m, int k, int n, int nnz, const int* row_indices, const VT* value
   const unsigned gy = (n + kTileCols - 1) / kTileCols;
   if (gy > 65535u) return IEX_ERR_UNSUPPORTED;
   dim3 grid((m + kRowsPerBlock - 1) / kRowsPerBlock, gy, batch);
-  spmm_rowgroup_kernel<VT, IT, LPR, NVEC, VS, VDN><<<grid, 128, 0, stream>>>(
-      m, k, n, nnz, row_indices, values, vstride, row_offsets, cols, dense, bias, out,
-      accumulate);
-  return launch_status();
+  return launch_overlapped(spmm_rowgroup_kernel<VT, IT, LPR, NVEC, VS, VDN>, grid, dim3(128), 0, stream, m, k, n, nnz,
+                           row_indices, values, vstride, row_offsets, cols, dense, bias, out, accumulate);
 }
 
 template <typename VT, typename IT, bool VS>

@@ -39,6 +39,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace iex {
 namespace tc {
@@ -50,7 +51,6 @@ constexpr int A_ATOM_BYTES = BM * 128;    // [128 rows x 64 fp16]
 constexpr int A_STAGE_BYTES = 2 * A_ATOM_BYTES;
 constexpr int kFirstDecodeWarp = 6;
 constexpr int kDecodeWarps = 16;          // CSR decoder warps of the sparse-capable instance
-constexpr uint32_t kSpinLimit = 1u << 23;  // mbarrier polls (with back-off) before a wait gives up
 constexpr int kMaxPeers = 8;              // GPUs of one box
 constexpr int kMaxStages = 6;             // dense stages (barrier slots reserved)
 constexpr int kMaxASlots = 8;             // sparse A slots of 64 columns (a power of two)
@@ -94,117 +94,6 @@ struct Params {
 };
 
 __device__ int g_status = 0;  // last device-side failure (IEX_ERR_TIMEOUT) of this library
-
-// ---------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {  // never suspends
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait with back-off.  A waiting warp sleeps `sleep_ns` between polls so that it
-// does not take issue slots from the warps doing the work.  Returns false when the wait
-// gave up or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, unsigned sleep_ns) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i >= 2u) __nanosleep(sleep_ns);
-    if ((i & 63u) == 63u && *abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicExch(status, IEX_ERR_TIMEOUT);
-  atomicExch(&g_status, IEX_ERR_TIMEOUT);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-      "l"(map), "r"(bar), "r"(c0), "r"(c1)
-      : "memory");
-}
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
-                                         uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
-// lbo/sbo in bytes.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) |
-         (static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16) |
-         (static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
-}
-
-// Descriptor of an operand `bytes` further on in shared memory: only the 14-bit address field
-// (bits 0-13, in units of 16 bytes) changes, and it cannot carry out of the field because all
-// of shared memory lies below 256 KB.  One 32-bit add per tensor-core instruction instead of
-// rebuilding the descriptor: the thread that issues them is a serial bottleneck of a unit.
-__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) {
-  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
-  return (desc & 0xFFFFFFFF00000000ull) | lo;
-}
 
 // Position u of the work list -> (is_sparse, tile, part).  With S = s_tiles * s_parts sparse
 // units and D = d_tiles * d_parts dense units the list is
@@ -493,7 +382,6 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
     *abort_flag = 1;
     atomicExch(prm.status, IEX_ERR_TIMEOUT);
-    atomicExch(&g_status, IEX_ERR_TIMEOUT);
     return false;
   };
 

@@ -17,6 +17,10 @@ module only loads it.  Operators:
   csr_to_dense_half(row_offsets, values, column_indices, m, k)  dense copy of a CSR matrix
   validate_csr(row_offsets, column_indices, m, k, require_ascending) -> int
                                                                 0, or IEX_CSR_* bits
+  sddmm_plan(row_offsets, column_indices, m, n)                 pattern-only plan (build once)
+  sddmm_tc_planned(a, b, plan, nnz)                             SDDMM on tensor cores (fp32,
+                                                                TF32 head/tail tiles), a [m, k],
+                                                                b [n, k] -> [nnz]
 With ``IEX_VALIDATE_CSR=1`` in the environment every sparse operator runs that check on its
 arguments first and raises on a malformed matrix (debugging aid; one extra kernel and a
 synchronisation per call).
@@ -50,4 +54,6 @@ OP_NAMES = (
     "fused_spmm_linear_half",
     "csr_to_dense_half",
     "validate_csr",
+    "sddmm_plan",
+    "sddmm_tc_planned",
 )

@@ -1,10 +1,11 @@
 """``MyLinear`` — the dense branch as an autograd operator: ``input @ weight.T``.
 
 Same arguments as intrasm_engine/pytorch/cpp_extensions/layers_and_funcs/torch.py:6-31
-(``weight`` is ``[out_features, in_features]`` as in ``torch.nn.Linear``).  fp16 inputs whose
-shape the tcgen05 kernel takes (tokens a multiple of 16 up to 256, in_features a multiple
-of 8) run on it; anything else is a plain library GEMM through ``torch.mm``, which is what
-the reference always does (:17).  The backward pass is the reference's two matmuls.
+(``weight`` is ``[out_features, in_features]`` as in ``torch.nn.Linear``).  fp16 inputs with
+in_features a multiple of 8 run on the tcgen05 kernel, whatever the token count (blocks of
+up to 256 tokens, a ragged tail padded); other dtypes (the reference's ``MyLinear`` is
+dtype-agnostic, :17) are a plain library GEMM through ``torch.mm``.  The backward pass is
+the reference's two matmuls.
 """
 from __future__ import annotations
 
@@ -15,8 +16,10 @@ from .utils import MyAutogradFunc, captured
 
 
 def tc_linear_eligible(input: torch.Tensor, weight: torch.Tensor) -> bool:
+    """fp16, any token count (the operator runs blocks of up to 256 tokens and pads a ragged
+    tail), in_features a multiple of 8, 16-byte aligned contiguous operands."""
     return (input.is_cuda and input.dtype == torch.float16 and weight.dtype == torch.float16
-            and input.dim() == 2 and input.size(0) % 16 == 0 and 0 < input.size(0) <= 256
+            and input.dim() == 2 and input.size(0) > 0
             and input.size(1) % 8 == 0 and input.is_contiguous() and weight.is_contiguous()
             and input.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 

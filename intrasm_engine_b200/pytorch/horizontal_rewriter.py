@@ -213,25 +213,35 @@ def _replay(constructor: TorchCUDAGraphConstructor):
 
 
 class CUDAGraphModulePreviousLayerFunction(torch.autograd.Function):
-    """Sits before a recorded layer; its backward replays the backward constructor's graph."""
+    """Sits before a recorded layer; its backward replays the backward constructor's graph.
+
+    The recorded layer's backward only RECORDS its kernels (autograd runs it just before this
+    node), so the gradient tensors that arrive here exist but hold nothing yet, and nothing
+    eager may touch them before the replay.  A layer that needs its input in two layouts
+    (``with_transposed``: the activation and its transposed copy, as the sparse and the dense
+    branch take them) therefore gets both from this node, whose backward adds the two
+    gradients AFTER the replay instead of leaving the sum to autograd.
+    """
 
     @staticmethod
-    def forward(ctx, backward_constructor, *inputs):
+    def forward(ctx, backward_constructor, x, with_transposed=False):
         ctx.backward_constructor = backward_constructor
-        return inputs if len(inputs) > 1 else inputs[0]
+        ctx.with_transposed = bool(with_transposed)
+        if ctx.with_transposed:
+            return x.view_as(x), x.t().contiguous()
+        return x.view_as(x)
 
     @staticmethod
     def backward(ctx, *grads):
         bc = ctx.backward_constructor
         if bc is not None and bc.node_count()[0] > 0:
-            # The recorded layer's backward has only RECORDED its kernels (autograd ran it just
-            # before this node): the gradient tensors exist, their contents do not.  Bring the
-            # side streams back to the primary one and run the graph now, before the gradients
-            # travel further up.
-            if len(bc.registeredStreams) > 1:
+            if len(bc.registeredStreams) > 1:  # bring the side streams back to the primary one
                 bc.join(bc.registeredStreams[1:], bc.registeredStreams[0])
             _replay(bc)
-        return (None, *grads)
+        g = grads[0]
+        if ctx.with_transposed and len(grads) > 1 and grads[1] is not None:
+            g = grads[1].t() if g is None else g + grads[1].t()
+        return None, g, None
 
 
 class CUDAGraphModuleNextLayerFunction(torch.autograd.Function):
@@ -281,7 +291,9 @@ class SparseDenseLayer(ModuleToReplay):
         self.mode = mode
         self.pair = make_kernel_pair_or_triple_autograd_function(MySpMM, MyLinear)
 
-    def forward(self, x, forward_constructors=None, backward_constructors=None):
+    wants_transposed_input = True  # ConstructorEnabledLayer hands over (x, x.t().contiguous())
+
+    def forward(self, x, xt=None, forward_constructors=None, backward_constructors=None):
         args = (x, self.row_indices, self.values, self.row_offsets, self.column_indices, self.m,
                 self.transp_info, x.t(), self.weight_dense)
         if self.mode == "fused":
@@ -296,7 +308,8 @@ class SparseDenseLayer(ModuleToReplay):
             for c in (ctor, bctor):
                 if c is not None and len(c.registeredStreams) < 2:
                     c.register_new_stream()
-            xt = x.t().contiguous()
+            if xt is None:
+                xt = x.t().contiguous()
             args = args[:7] + (xt, self.weight_dense)
             # Without a backward constructor the backward pass runs eagerly (the operators
             # check for None); with one, both operators record their backward kernels on its
@@ -325,9 +338,14 @@ class ConstructorEnabledLayer(nn.Module):
         n = self.layer_to_replay.num_parallel_autograd_funcs
         backward_constructors = [TorchCUDAGraphConstructor() for _ in range(n)]
         forward_constructors = [TorchCUDAGraphConstructor() for _ in range(n)]
-        x = CUDAGraphModulePreviousLayerFunction.apply(backward_constructors[0], x)
-        outs = self.layer_to_replay(x, forward_constructors=forward_constructors,
-                                    backward_constructors=backward_constructors)
+        if getattr(self.layer_to_replay, "wants_transposed_input", False):
+            x, xt = CUDAGraphModulePreviousLayerFunction.apply(backward_constructors[0], x, True)
+            outs = self.layer_to_replay(x, xt, forward_constructors=forward_constructors,
+                                        backward_constructors=backward_constructors)
+        else:
+            x = CUDAGraphModulePreviousLayerFunction.apply(backward_constructors[0], x)
+            outs = self.layer_to_replay(x, forward_constructors=forward_constructors,
+                                        backward_constructors=backward_constructors)
         outs = outs if isinstance(outs, tuple) else (outs,)
         recorded = forward_constructors[0] if forward_constructors[0].node_count()[0] > 1 else None
         outs = CUDAGraphModuleNextLayerFunction.apply(recorded, *outs)

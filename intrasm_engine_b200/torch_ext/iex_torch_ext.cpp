@@ -80,9 +80,7 @@ bool validation_enabled() {
 void maybe_validate(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t k,
                     const at::Tensor* row_indices, bool require_ascending) {
   if (!validation_enabled()) return;
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  cudaStreamIsCapturing(at::cuda::getCurrentCUDAStream(row_offsets.get_device()).stream(), &cap);
-  if (cap != cudaStreamCaptureStatusNone) return;
+  if (iex_stream_is_capturing(stream_of(row_offsets))) return;
   const int64_t code = validate_csr_impl(row_offsets, column_indices, m, k, row_indices, require_ascending);
   TORCH_CHECK(code == 0, "malformed CSR argument (IEX_CSR_* bits ", code,
               "): 1 first offset, 2 last offset, 4 offsets not monotone, 8 column out of range, "
@@ -199,16 +197,10 @@ at::Tensor sddmm_sputnik_atomic_upd_weight(const at::Tensor& a, const at::Tensor
   return out;
 }
 
-// Dense branch on tensor cores: input @ weight^T (layers_and_funcs/torch.py:17)
-at::Tensor linear_fp16(const at::Tensor& input, const at::Tensor& weight) {
-  TORCH_CHECK(input.dim() == 2 && weight.dim() == 2, "input and weight must be 2-D");
-  TORCH_CHECK(input.size(1) == weight.size(1), "input and weight disagree on in_features");
-  check_common({{"input", &input}, {"weight", &weight}});
-  TORCH_CHECK(input.scalar_type() == at::kHalf && weight.scalar_type() == at::kHalf,
-              "input and weight must be float16");
-  c10::cuda::CUDAGuard guard(input.device());
+// One block of at most 256 tokens (a multiple of 16) of the dense branch into `out` (a
+// contiguous [tokens, out_features] block).
+void linear_block(const at::Tensor& input, const at::Tensor& weight, at::Tensor out) {
   const int64_t tokens = input.size(0), out_features = weight.size(0);
-  at::Tensor out = at::empty({tokens, out_features}, input.options());
   // A weight with few 128-row tiles would leave most SMs without work: split every tile's K
   // range over about 128 / tiles CTAs (measured optimum on B200: 32 tiles -> 4 parts,
   // 4 tiles -> 16).  The partial tiles live in a scratch tensor of the caching allocator.
@@ -222,11 +214,38 @@ at::Tensor linear_fp16(const at::Tensor& input, const at::Tensor& weight) {
                                        weight.data_ptr(), out.data_ptr(), parts, scratch.data_ptr(), need,
                                        stream_of(input)),
                  "iex_linear_f16_splitk");
-    return out;
+    return;
   }
   check_status(iex_linear_f16(tokens, input.size(1), out_features, input.data_ptr(), weight.data_ptr(),
                               out.data_ptr(), stream_of(input)),
                "iex_linear_f16");
+}
+
+// Dense branch on tensor cores: input @ weight^T (layers_and_funcs/torch.py:17).  Any number
+// of tokens: the kernel takes up to 256 at a time (a multiple of 16), so longer inputs run
+// block after block into the rows of one output, and a ragged tail is padded with zero rows.
+at::Tensor linear_fp16(const at::Tensor& input, const at::Tensor& weight) {
+  TORCH_CHECK(input.dim() == 2 && weight.dim() == 2, "input and weight must be 2-D");
+  TORCH_CHECK(input.size(1) == weight.size(1), "input and weight disagree on in_features");
+  check_common({{"input", &input}, {"weight", &weight}});
+  TORCH_CHECK(input.scalar_type() == at::kHalf && weight.scalar_type() == at::kHalf,
+              "input and weight must be float16");
+  c10::cuda::CUDAGuard guard(input.device());
+  const int64_t tokens = input.size(0), out_features = weight.size(0), in_features = input.size(1);
+  at::Tensor out = at::empty({tokens, out_features}, input.options());
+  if (tokens == 0 || out_features == 0) return out;
+  const int64_t whole = tokens / 16 * 16;
+  for (int64_t t0 = 0; t0 < whole; t0 += 256) {
+    const int64_t block = std::min<int64_t>(256, whole - t0);
+    linear_block(input.narrow(0, t0, block), weight, out.narrow(0, t0, block));
+  }
+  if (whole < tokens) {  // ragged tail: 16 rows, the missing ones zero
+    at::Tensor tail_in = at::zeros({16, in_features}, input.options());
+    tail_in.narrow(0, 0, tokens - whole).copy_(input.narrow(0, whole, tokens - whole));
+    at::Tensor tail_out = at::empty({16, out_features}, input.options());
+    linear_block(tail_in, weight, tail_out);
+    out.narrow(0, whole, tokens - whole).copy_(tail_out.narrow(0, 0, tokens - whole));
+  }
   return out;
 }
 
@@ -298,6 +317,42 @@ at::Tensor csr_to_dense_half(const at::Tensor& row_offsets, const at::Tensor& va
   return out;
 }
 
+// Plan of a sparsity pattern for the tensor-core SDDMM (pattern-only, like row_indices:
+// build once per pattern, reuse for every product on it).  Returns an opaque uint8 tensor.
+at::Tensor sddmm_plan(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t n) {
+  check_common({{"row_offsets", &row_offsets}, {"column_indices", &column_indices}});
+  TORCH_CHECK(row_offsets.scalar_type() == at::kInt && column_indices.scalar_type() == at::kInt,
+              "index tensors must be int32");
+  TORCH_CHECK(row_offsets.dim() == 1 && row_offsets.size(0) == m + 1, "row_offsets must have m + 1 entries");
+  c10::cuda::CUDAGuard guard(row_offsets.device());
+  const int64_t nnz = column_indices.numel();
+  const size_t bytes = iex_sddmm_plan_bytes(m, n, nnz);
+  at::Tensor plan = at::empty({static_cast<int64_t>(std::max<size_t>(bytes, 16))},
+                              row_offsets.options().dtype(at::kByte));
+  check_status(iex_sddmm_plan_build(m, n, nnz, row_offsets.data_ptr<int>(), column_indices.data_ptr<int>(),
+                                    plan.data_ptr(), bytes, stream_of(row_offsets)),
+               "iex_sddmm_plan_build");
+  return plan;
+}
+
+// SDDMM on tensor cores with a plan from sddmm_plan: a [m, k] and b [n, k] fp32 -> [nnz] in
+// storage order (the result contract of sddmm_sputnik_atomic_upd_weight with batch 1)
+at::Tensor sddmm_tc_planned(const at::Tensor& a, const at::Tensor& b, const at::Tensor& plan, int64_t nnz) {
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "a must be [m, k] and b [n, k]");
+  check_common({{"a", &a}, {"b", &b}, {"plan", &plan}});
+  TORCH_CHECK(a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat, "a and b must be float32");
+  TORCH_CHECK(plan.scalar_type() == at::kByte, "plan must come from sddmm_plan");
+  const int64_t m = a.size(0), k = a.size(1), n = b.size(0);
+  TORCH_CHECK(static_cast<size_t>(plan.numel()) >= iex_sddmm_plan_bytes(m, n, nnz),
+              "plan was built for another pattern size");
+  c10::cuda::CUDAGuard guard(a.device());
+  at::Tensor out = at::empty({nnz}, a.options());
+  check_status(iex_sddmm_f32_tc(m, k, n, nnz, plan.data_ptr(), a.data_ptr<float>(), b.data_ptr<float>(),
+                                out.data_ptr<float>(), 0, stream_of(a)),
+               "iex_sddmm_f32_tc");
+  return out;
+}
+
 // 0 when the CSR is well formed, else the OR of the IEX_CSR_* bits (include/iex_b200.h)
 int64_t validate_csr(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t k,
                      bool require_ascending) {
@@ -317,6 +372,8 @@ TORCH_LIBRARY(iex_ops, m) {
   m.def("fused_spmm_linear_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, int m, Tensor weight) -> (Tensor, Tensor)");
   m.def("csr_to_dense_half(Tensor row_offsets, Tensor values, Tensor column_indices, int m, int k) -> Tensor");
   m.def("validate_csr(Tensor row_offsets, Tensor column_indices, int m, int k, bool require_ascending) -> int");
+  m.def("sddmm_plan(Tensor row_offsets, Tensor column_indices, int m, int n) -> Tensor");
+  m.def("sddmm_tc_planned(Tensor a, Tensor b, Tensor plan, int nnz) -> Tensor");
 }
 
 // CUDA dispatch key only: a CPU tensor reaches no implementation (there is no CPU path).
@@ -330,4 +387,6 @@ TORCH_LIBRARY_IMPL(iex_ops, CUDA, m) {
   m.impl("fused_spmm_linear_half", &fused_spmm_linear_half);
   m.impl("csr_to_dense_half", &csr_to_dense_half);
   m.impl("validate_csr", &validate_csr);
+  m.impl("sddmm_plan", &sddmm_plan);
+  m.impl("sddmm_tc_planned", &sddmm_tc_planned);
 }

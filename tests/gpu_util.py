@@ -107,3 +107,36 @@ def sddmm_f32(mask: DevCSR, lhs, rhs, out=None, accumulate=False):
               ptr(mask.column_indices), ptr(lhs), ptr(rhs), ptr(out), batch, int(accumulate),
               stream_ptr())
     return out
+
+
+def sddmm_plan(mask: DevCSR, n):
+    """Plan of the pattern for the tensor-core SDDMM (iex_sddmm_plan_build); an opaque buffer."""
+    nbytes = _lib.lib.iex_sddmm_plan_bytes(mask.m, n, mask.nnz)
+    plan = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=DEV)
+    _lib.call("iex_sddmm_plan_build", mask.m, n, mask.nnz, ptr(mask.row_offsets), ptr(mask.column_indices),
+              ptr(plan), nbytes, stream_ptr())
+    return plan
+
+
+def sddmm_f32_tc(mask: DevCSR, lhs2d, rhs2d, out=None, accumulate=False, plan=None):
+    """Raw iex_sddmm_f32_tc call (tensor cores; batch 1): lhs [m, k], rhs [n, k] device fp32."""
+    m, k = lhs2d.shape
+    n = rhs2d.shape[0]
+    if plan is None:
+        plan = sddmm_plan(mask, n)
+    if out is None:
+        out = torch.empty((mask.nnz,), dtype=torch.float32, device=DEV)
+    _lib.call("iex_sddmm_f32_tc", m, k, n, mask.nnz, ptr(plan), ptr(lhs2d), ptr(rhs2d), ptr(out),
+              int(accumulate), stream_ptr())
+    return out
+
+
+def sddmm_close(got, exact, sum_abs):
+    """The fp32 bar of the task (1e-5 relative) with the error measured against the sum of the
+    terms' magnitudes, which is what a dot product's rounding error scales with:
+    |got - exact| <= 1e-5 * |exact| + 2e-6 * sum_k |lhs||rhs|."""
+    got = np.asarray(got, dtype=np.float64)
+    exact = np.asarray(exact, dtype=np.float64)
+    if exact.size == 0:
+        return got.size == 0
+    return bool(np.all(np.abs(got - exact) <= 1e-5 * np.abs(exact) + 2e-6 * np.asarray(sum_abs, np.float64)))

@@ -103,3 +103,152 @@ def test_torch_ops_sddmm(oracle):
     with pytest.raises(RuntimeError):
         torch.ops.iex_ops.sddmm_sputnik_atomic_upd_weight(G.dev(q)[None], G.dev(k[:, :16])[None],
                                                           dm.row_indices, dm.row_offsets, dm.column_indices)
+
+
+# ----------------------------------------------------------------------------------------
+# Tensor-core SDDMM (iex_sddmm_plan_build + iex_sddmm_f32_tc): dense 128 x 128 tiles in TF32
+# head/tail arithmetic, sampled at the stored positions through a plan of the pattern.  Same
+# bar as the CUDA-core kernel (1e-5 against the double-precision oracle), plus a bound relative
+# to the sum of the terms' magnitudes, the output order through a position-dependent
+# reference, exact small-integer cases, and the plan itself against a host-side regrouping.
+# ----------------------------------------------------------------------------------------
+
+def _tc_case(rng, m, n, k, row_density):
+    mask = syn.csr_from_mask(rng.random((m, n)) < np.asarray(row_density).reshape(-1, 1), rng=rng)
+    lhs = rng.standard_normal((m, k)).astype(np.float32)
+    rhs = rng.standard_normal((n, k)).astype(np.float32)
+    return mask, lhs, rhs
+
+
+def _check_tc(oracle, mask, lhs, rhs):
+    from intrasm_engine_b200 import _lib
+    got = G.sddmm_f32_tc(G.DevCSR(mask), G.dev(lhs), G.dev(rhs)).cpu().numpy()
+    torch.cuda.synchronize()
+    assert _lib.lib.iex_last_device_status(1) == 0
+    exact = oracle.sddmm(lhs[None], rhs[None], mask.row_indices, mask.row_offsets, mask.column_indices, f64=True)
+    sabs = oracle.sddmm(np.abs(lhs)[None], np.abs(rhs)[None], mask.row_indices, mask.row_offsets,
+                        mask.column_indices, f64=True)
+    assert got.shape == exact.shape
+    assert G.close(got, exact, 1e-5, 1e-5), G.max_violation(got, exact, 1e-5, 1e-5)
+    assert G.sddmm_close(got, exact, sabs)
+    return got
+
+
+@pytest.mark.parametrize("m,n,k,density", [
+    (128, 128, 64, 0.1), (128, 128, 32, 0.5), (1, 1, 32, 1.0), (130, 257, 64, 0.2), (300, 1000, 64, 0.05),
+    (1000, 300, 32, 0.05), (256, 4096, 64, 0.02), (2048, 512, 64, 0.3), (129, 129, 64, 1.0),
+    (640, 640, 64, 0.0), (20000, 256, 32, 0.03),
+])
+def test_sddmm_tc_shapes(oracle, m, n, k, density):
+    rng = np.random.default_rng(m + 3 * n + 7 * k)
+    mask, lhs, rhs = _tc_case(rng, m, n, k, np.full(m, density))
+    _check_tc(oracle, mask, lhs, rhs)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_sddmm_tc_random_shapes(oracle, seed):
+    """Ragged rows in one matrix -- empty, a few entries, completely full (tiles with more
+    entries than the epilogue threads keep in registers) -- and sizes that are not multiples
+    of the tile."""
+    rng = np.random.default_rng(900 + seed)
+    m, n = int(rng.integers(1, 1500)), int(rng.integers(1, 1500))
+    k = int(rng.choice([32, 64]))
+    row_density = rng.choice([0.0, 0.01, 0.05, 0.3, 1.0], size=m, p=[0.1, 0.2, 0.4, 0.2, 0.1])
+    mask, lhs, rhs = _tc_case(rng, m, n, k, row_density)
+    _check_tc(oracle, mask, lhs, rhs)
+
+
+@pytest.mark.parametrize("m,n,density", [(300, 500, 0.1), (129, 1000, 0.6), (1, 1, 1.0), (700, 64, 0.02)])
+def test_sddmm_plan_regroups_positions_by_tile(m, n, density):
+    """The plan against the same regrouping done on the host: per 128 x 128 tile the stored
+    positions in storage order, with their row / column inside the tile."""
+    from intrasm_engine_b200 import _lib
+    rng = np.random.default_rng(m + n)
+    mask = syn.csr_from_mask(rng.random((m, n)) < density, rng=rng)
+    dm = G.DevCSR(mask)
+    plan = G.sddmm_plan(dm, n).cpu().numpy()
+    bands, T = (m + 127) // 128, (n + 127) // 128
+    ntiles, nnz = bands * T, mask.nnz
+    up16 = lambda x: (x + 15) & ~15
+    tile_ptr = plan[:4 * (ntiles + 1)].view(np.int32)
+    o_dest = up16(4 * (ntiles + 1))
+    dest = plan[o_dest:o_dest + 4 * nnz].view(np.int32)
+    o_entry = o_dest + up16(4 * nnz)
+    entry = plan[o_entry:o_entry + 2 * nnz].view(np.uint16)
+    assert _lib.lib.iex_sddmm_plan_bytes(m, n, nnz) == o_entry + up16(2 * nnz) + up16(4 * ntiles * 128)
+    rows = np.repeat(np.arange(m), np.diff(mask.row_offsets))
+    cols = mask.column_indices.astype(np.int64)
+    tile = (rows // 128) * T + cols // 128
+    order = np.argsort(tile, kind="stable")  # storage order kept inside a tile
+    np.testing.assert_array_equal(dest, order.astype(np.int32))
+    np.testing.assert_array_equal(entry, (((rows % 128) << 7) | (cols % 128))[order].astype(np.uint16))
+    np.testing.assert_array_equal(tile_ptr, np.concatenate([[0], np.cumsum(np.bincount(tile, minlength=ntiles))]))
+
+
+def test_sddmm_tc_output_order_and_accumulate(oracle):
+    """lhs = one-hot rows and rhs = small integers make out[p] a function of (row(p), col[p])
+    alone, exactly: the output must be aligned with column_indices."""
+    rng = np.random.default_rng(3)
+    m, n, k = 300, 500, 64
+    mask = syn.csr_from_mask(rng.random((m, n)) < 0.1, rng=rng)
+    lhs = np.zeros((m, k), np.float32)
+    lhs[np.arange(m), np.arange(m) % k] = 1.0 + np.arange(m) // k
+    rhs = rng.integers(-8, 9, size=(n, k)).astype(np.float32)
+    dm = G.DevCSR(mask)
+    plan = G.sddmm_plan(dm, n)
+    got = G.sddmm_f32_tc(dm, G.dev(lhs), G.dev(rhs), plan=plan).cpu().numpy()
+    rows = np.repeat(np.arange(m), np.diff(mask.row_offsets))
+    expect = (1.0 + rows // k) * rhs[mask.column_indices, rows % k]
+    np.testing.assert_array_equal(got, expect.astype(np.float32))
+    start = torch.full((mask.nnz,), 2.0, device=G.DEV)
+    acc = G.sddmm_f32_tc(dm, G.dev(lhs), G.dev(rhs), out=start, accumulate=True, plan=plan).cpu().numpy()
+    np.testing.assert_array_equal(acc, (expect + 2.0).astype(np.float32))
+
+
+def test_sddmm_tc_exact_on_small_integers(oracle):
+    """Integers of a few bits are exact in TF32 and their sums in fp32: bit-exact results."""
+    rng = np.random.default_rng(8)
+    m, n, k = 700, 900, 64
+    mask = syn.csr_from_mask(rng.random((m, n)) < 0.07, rng=rng)
+    lhs = rng.integers(-7, 8, size=(m, k)).astype(np.float32)
+    rhs = rng.integers(-7, 8, size=(n, k)).astype(np.float32)
+    got = G.sddmm_f32_tc(G.DevCSR(mask), G.dev(lhs), G.dev(rhs)).cpu().numpy()
+    exact = oracle.sddmm(lhs[None], rhs[None], mask.row_indices, mask.row_offsets, mask.column_indices, f64=True)
+    np.testing.assert_array_equal(got, exact.astype(np.float32))
+
+
+def test_sddmm_tc_cfg2_full_size_and_agreement_with_cuda_cores(oracle):
+    """Benchmark configuration 2 on the tensor-core kernel: against the double-precision
+    oracle, the torch CPU path, and the CUDA-core kernel; deterministic from run to run; the
+    torch operators give the same bits."""
+    mask, q, k, _v = syn.sddmm_chain_case(0)
+    dm = G.DevCSR(mask)
+    got = _check_tc(oracle, mask, q, k)
+    tref = oracle.torch_sddmm(q, k, mask.row_offsets, mask.column_indices)
+    assert G.close(got, tref, 1e-5, 1e-5)
+    simt = G.sddmm_f32(dm, G.dev(q)[None], G.dev(k)[None])
+    tc2 = G.sddmm_f32_tc(dm, G.dev(q), G.dev(k))
+    assert torch.equal(tc2.cpu(), torch.as_tensor(got))
+    assert G.close(tc2.cpu().numpy(), simt.cpu().numpy(), 1e-5, 1e-5)
+    import intrasm_engine_b200  # noqa: F401
+    ops = torch.ops.iex_ops
+    plan = ops.sddmm_plan(dm.row_offsets, dm.column_indices, 4096, 4096)
+    assert torch.equal(ops.sddmm_tc_planned(G.dev(q), G.dev(k), plan, mask.nnz), tc2)
+
+
+def test_sddmm_tc_takes_unsorted_columns_and_rejects_unsupported(oracle):
+    """The plan keeps storage order whatever the order of the columns inside a row."""
+    from intrasm_engine_b200 import _lib
+    rng = np.random.default_rng(4)
+    mask, lhs, rhs = _tc_case(rng, 256, 512, 64, np.full(256, 0.1))
+    for r in range(256):  # shuffle every row's columns
+        b, e = mask.row_offsets[r], mask.row_offsets[r + 1]
+        mask.column_indices[b:e] = rng.permutation(mask.column_indices[b:e])
+    _check_tc(oracle, mask, lhs, rhs)
+    with pytest.raises(_lib.IexError) as e:
+        G.sddmm_f32_tc(G.DevCSR(mask), G.dev(lhs[:, :48].copy()), G.dev(rhs[:, :48].copy()))
+    assert e.value.status == -2
+    assert _lib.lib.iex_sddmm_f32_tc_supported(256, 64, 512, 1) == 1
+    assert _lib.lib.iex_sddmm_f32_tc_supported(256, 64, 512, 2) == 0
+    assert _lib.lib.iex_sddmm_f32_prefers_tc(4096, 64, 4096, 838861, 1) == 1
+    assert _lib.lib.iex_sddmm_f32_prefers_tc(4096, 64, 4096, 20000, 1) == 0
