@@ -86,7 +86,12 @@ def build_torch_ext(force: bool = False) -> str:
     torch_dir = os.path.dirname(torch.__file__)
     torch_lib = os.path.join(torch_dir, "lib")
     torch_inc = os.path.join(torch_dir, "include")
-    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared",
+    # The system g++ on PATH, not $CXX: the extension must share the process's libstdc++.so with
+    # torch.  A toolchain that links its own static C++ runtime into the extension gives the
+    # process two exception runtimes, and an error raised by TORCH_CHECK then crashes while
+    # unwinding through the extension's frames.  IEX_CXX overrides.
+    cxx = os.environ.get("IEX_CXX") or shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared",
            f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
            "-I", os.path.join(REPO_DIR, "include"),
            "-I", torch_inc, "-I", os.path.join(torch_inc, "torch", "csrc", "api", "include"),

@@ -64,6 +64,16 @@ def test_torch_extension_is_a_compiled_library():
     assert raw is not None
 
 
+def test_torch_extension_shares_the_process_cxx_runtime():
+    """The extension must not carry its own copy of the C++ exception runtime (a toolchain that
+    links libstdc++ statically does that): errors raised by its argument checks are thrown in
+    torch's runtime and have to unwind through the extension's frames."""
+    import subprocess
+    from intrasm_engine_b200 import ops
+    out = subprocess.run(["nm", "-D", "--defined-only", ops.EXT_PATH], capture_output=True, text=True).stdout
+    assert "__cxa_allocate_exception" not in out and "__gxx_personality_v0" not in out
+
+
 def test_no_cpu_fallback():
     """CPU tensors are refused: the operators exist for CUDA only."""
     import pytest

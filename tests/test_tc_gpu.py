@@ -350,6 +350,15 @@ def test_torch_ops_tc(oracle):
     assert G.tc_close(out_s.cpu().numpy(), ref_s, sabs_s)
     with pytest.raises(RuntimeError):
         ops.linear_fp16(xs.t().contiguous().float(), ws)
+    # a shape the kernel family refuses at launch time surfaces as a Python error too
+    with pytest.raises(RuntimeError, match="not supported"):
+        ops.spmm_tc_half(xs[:, :48].contiguous(), da.row_offsets, da.values, da.column_indices, 256)
+    # more tokens than one kernel launch takes, and a ragged count: blocks of 256 + a padded tail
+    xl = torch.randn(600 + 7, 512, device=G.DEV).half()
+    big = ops.linear_fp16(xl, ws)
+    ref = xl.float() @ ws.float().t()
+    assert big.shape == (607, 384)
+    assert torch.allclose(big.float(), ref, rtol=2e-3, atol=2e-3 * float(ref.abs().max()))
 
 
 # ----------------------------------------------------------------------------------------
