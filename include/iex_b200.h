@@ -125,6 +125,33 @@ IEX_API int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, con
 IEX_API int iex_sddmm_f32_tc_supported(int m, int k, int n, int batch);
 IEX_API int iex_sddmm_f32_prefers_tc(int m, int k, int n, int nnz, int batch);
 
+/* The plan in general: stored positions regrouped by tile of 128 rows x tile_cols columns
+ * (tile_cols 64 or 128).  iex_sddmm_plan_* are these with tile_cols = 128; the tensor-core
+ * SpMM below takes tile_cols = 64.  No counterpart in the reference beyond row_indices. */
+IEX_API size_t iex_tile_plan_bytes(int m, int n, int nnz, int tile_cols);
+IEX_API int iex_tile_plan_build(int m, int n, int nnz, int tile_cols, const int32_t* row_offsets,
+                                const int32_t* column_indices, void* plan, size_t plan_bytes,
+                                void* stream);
+
+/* CSR SpMM on tensor cores, fp32 in and out: out [m, n] = A_csr [m, k] * dense [k, n]; same
+ * result contract as iex_spmm_f32 with batch = 1, shared values, no bias (replaces
+ * my_sputnik::CudaSpmm2 / CudaSpmm3, extensions.h:10-17).  A 128-row band of A is expanded, 64
+ * columns at a time, into a dense shared-memory operand (TF32 head and tail planes) and
+ * multiplied with the matching rows of `dense` by tcgen05.mma.kind::tf32; error below 2^-19 of
+ * sum |a||b|, summation order fixed (results do not depend on timing).
+ *   plan       a tile plan of A's pattern with tile_cols = 64 (iex_tile_plan_build(m, k, ...))
+ *   workspace  device memory, 16-byte aligned, iex_spmm_f32_tc_workspace_bytes(m, k, n) bytes
+ *              (0 for matrices of many bands): partial results of bands that are cut into
+ *              several units; a second small kernel adds them in unit order.
+ * Limits: n = 32 or 64; dense / out 16-byte aligned (else IEX_ERR_UNSUPPORTED).
+ * iex_spmm_f32_prefers_tc: whether this kernel is expected to beat the CUDA-core one. */
+IEX_API int iex_spmm_f32_tc(int m, int k, int n, int nnz, const void* plan, const float* values,
+                            const float* dense, float* out, void* workspace, size_t workspace_bytes,
+                            void* stream);
+IEX_API size_t iex_spmm_f32_tc_workspace_bytes(int m, int k, int n);
+IEX_API int iex_spmm_f32_tc_supported(int m, int k, int n);
+IEX_API int iex_spmm_f32_prefers_tc(int m, int k, int n, int nnz);
+
 /* ------------------------------------------------------------------------------------
  * Tensor-core (tcgen05 / TMEM / TMA) entry points, fp16 storage, fp32 accumulate.
  * Shared limits: n (tokens) a multiple of 16 (dense) / 64 (sparse, fused) and <= 256;

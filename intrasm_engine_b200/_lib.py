@@ -36,6 +36,15 @@ SIGNATURES = {
     "iex_sddmm_plan_bytes": (c_size, [c_int, c_int, c_int]),
     # m n nnz row_offsets cols plan plan_bytes stream
     "iex_sddmm_plan_build": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
+    # m n nnz tile_cols
+    "iex_tile_plan_bytes": (c_size, [c_int, c_int, c_int, c_int]),
+    # m n nnz tile_cols row_offsets cols plan plan_bytes stream
+    "iex_tile_plan_build": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
+    # m k n nnz plan values dense out workspace workspace_bytes stream
+    "iex_spmm_f32_tc": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_size, c_ptr]),
+    "iex_spmm_f32_tc_workspace_bytes": (c_size, [c_int, c_int, c_int]),
+    "iex_spmm_f32_tc_supported": (c_int, [c_int, c_int, c_int]),
+    "iex_spmm_f32_prefers_tc": (c_int, [c_int, c_int, c_int, c_int]),
     # m k n nnz plan lhs rhs out accumulate stream
     "iex_sddmm_f32_tc": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr]),
     "iex_sddmm_f32_tc_supported": (c_int, [c_int, c_int, c_int, c_int]),

@@ -43,6 +43,8 @@
 
 #include "common.cuh"
 #include "tc_ptx.cuh"
+#include "tc_prof.cuh"
+#include "tile_plan.cuh"
 
 namespace iex {
 namespace sddmm_tc {
@@ -67,20 +69,6 @@ constexpr int kBarBytes = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemAHi = 384, kTmemALo = 448;
 
-// Cycle accounting per role for tuning (clock64 laps into a caller-provided buffer); compiled
-// in only with -DIEX_SDDMM_PROFILE, never in the library build.
-#ifdef IEX_SDDMM_PROFILE
-__device__ __forceinline__ long long prof_ns() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define IEX_PROF_BEGIN long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t = clock64(); const long long prof_ns0 = prof_ns();
-#define IEX_LAP(slot) { const long long now_ = clock64(); prof_acc[slot] += now_ - prof_t; prof_t = now_; }
-#define IEX_PROF_DUMP(cond, base) if ((cond) && prm.prof) { for (int i_ = 0; i_ < 8; ++i_) prm.prof[blockIdx.x * 64 + (base) + i_] = prof_acc[i_]; \
-    if ((base) == 8) { prm.prof[blockIdx.x * 64 + 40] = prof_ns0; prm.prof[blockIdx.x * 64 + 41] = prof_ns(); } }
-#else
-#define IEX_PROF_BEGIN
-#define IEX_LAP(slot)
-#define IEX_PROF_DUMP(cond, base)
-#endif
-
 struct Params {
   int m, n, k, nnz;
   const int* tile_ptr;         // [bands * tiles_per_band + 1]
@@ -95,9 +83,7 @@ struct Params {
   // base_splits runs; CTA c takes units c, c + grid, ...
   int units, base_splits, bands_hi;
   int* status;
-#ifdef IEX_SDDMM_PROFILE
-  long long* prof;
-#endif
+  IEX_PROF_FIELD
 };
 
 __device__ __forceinline__ void unit_of(int u, const Params& p, int& band, int& t0, int& t1) {
@@ -213,9 +199,7 @@ __device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) {
 template <int KA>
 __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm) {
   extern __shared__ uint8_t smem_raw[];
-#ifdef IEX_SDDMM_PROFILE
-  if (threadIdx.x == 0 && prm.prof) prm.prof[blockIdx.x * 64 + 42] = prof_ns();
-#endif
+  IEX_PROF_STAMP(threadIdx.x == 0, 42)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr uint32_t kPlaneB = KA * kAtomBytesB;  // one hi or lo plane of a rhs tile
   auto b_hi = [&](int s) { return smem_base + static_cast<uint32_t>(s) * 2u * kPlaneB; };
@@ -264,9 +248,7 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
   // end of the kernel before this one in the stream; global memory comes next.
   grid_dependency_wait();
   grid_launch_dependents();
-#ifdef IEX_SDDMM_PROFILE
-  if (threadIdx.x == 0 && prm.prof) prm.prof[blockIdx.x * 64 + 43] = prof_ns();
-#endif
+  IEX_PROF_STAMP(threadIdx.x == 0, 43)
 
   const int k = prm.k;
   constexpr int kv_shift = KA == 1 ? 3 : 4;  // log2(float4 per row)
@@ -502,9 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                  : "memory");
-#ifdef IEX_SDDMM_PROFILE
-    if (lane == 0 && prm.prof) prm.prof[blockIdx.x * 64 + 44] = prof_ns();
-#endif
+    IEX_PROF_STAMP(lane == 0, 44)
   }
 }
 
@@ -534,163 +514,8 @@ int launch(Params prm, cudaStream_t stream) {
   return launch_overlapped(kern, dim3(grid), dim3(kThreads), smem, stream, prm);
 }
 
-// ---------------------------------------------------------------------------------------
-// Plan: the stored positions regrouped by 128 x 128 tile (a counting sort that keeps the
-// storage order inside a tile).  Three small kernels on the caller's stream:
-//   count   one warp per row walks the row's indices and adds, per tile the row touches, the
-//           number of its entries there into counts[tile][row in band]   (indices need not
-//           ascend)
-//   scan    one block: exclusive prefix sum over counts in (tile, row) order -> where each
-//           (tile, row) run starts; tile_ptr[tile] = the start of its first row
-//   fill    one warp per row again: every entry goes to its run, in storage order
-// counts / starts live in the plan's own scratch part.
-// ---------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) plan_count_kernel(int m, int T, const int* __restrict__ row_offsets,
-                                                         const int* __restrict__ cols, int* __restrict__ cells) {
-  const int lane = threadIdx.x & 31;
-  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (row >= m) return;
-  const int band = row >> 7, rl = row & 127;
-  const int beg = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
-  for (int p = beg + lane; p < end; p += 32) {
-    const int t = __ldg(cols + p) >> 7;
-    if (t >= 0 && t < T) atomicAdd(cells + (static_cast<size_t>(band) * T + t) * TM + rl, 1);
-  }
-}
-
-// cells[tile][row] : count -> exclusive start (in place); tile_ptr[tile]; one block of 1024.
-__global__ void __launch_bounds__(1024) plan_scan_kernel(int ncells, int ntiles, int* __restrict__ cells,
-                                                         int* __restrict__ tile_ptr) {
-  __shared__ int warp_sums[32];
-  __shared__ int carry_s;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) carry_s = 0;
-  __syncthreads();
-  for (int base = 0; base < ncells; base += 1024) {
-    const int i = base + threadIdx.x;
-    const int v = i < ncells ? cells[i] : 0;
-    int x = v;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int y = __shfl_up_sync(0xffffffffu, x, d);
-      if (lane >= d) x += y;
-    }
-    if (lane == 31) warp_sums[warp] = x;
-    __syncthreads();
-    if (warp == 0) {
-      int w = warp_sums[lane];
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int y = __shfl_up_sync(0xffffffffu, w, d);
-        if (lane >= d) w += y;
-      }
-      warp_sums[lane] = w;
-    }
-    __syncthreads();
-    const int incl = x + (warp > 0 ? warp_sums[warp - 1] : 0) + carry_s;
-    if (i < ncells) {
-      cells[i] = incl - v;
-      if ((i & (TM - 1)) == 0) tile_ptr[i >> 7] = incl - v;
-    }
-    __syncthreads();
-    if (threadIdx.x == 1023) carry_s = incl;
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) tile_ptr[ntiles] = carry_s;
-}
-
-__global__ void __launch_bounds__(256) plan_fill_kernel(int m, int T, const int* __restrict__ row_offsets,
-                                                        const int* __restrict__ cols, int* __restrict__ cells,
-                                                        uint16_t* __restrict__ entry, int* __restrict__ dest) {
-  const int lane = threadIdx.x & 31;
-  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (row >= m) return;
-  const int band = row >> 7, rl = row & 127;
-  const int beg = __ldg(row_offsets + row), end = __ldg(row_offsets + row + 1);
-  // Entries of one row and one tile keep their storage order: within a pass of 32 entries a
-  // lane's rank among the lanes of the same tile comes from a match mask, and the warp bumps
-  // the cell's running start once per tile and pass.
-  for (int p0 = beg; p0 < end; p0 += 32) {
-    const int p = p0 + lane;
-    const bool on = p < end;
-    const int c = on ? __ldg(cols + p) : -1;
-    const int t = c >> 7;
-    const bool ok = on && t >= 0 && t < T;
-    const unsigned peers = __match_any_sync(0xffffffffu, ok ? t : -1 - lane);
-    if (ok) {
-      int* cell = cells + (static_cast<size_t>(band) * T + t) * TM + rl;
-      const int rank = __popc(peers & ((1u << lane) - 1u));
-      const int leader = __ffs(peers) - 1;
-      int start = 0;
-      if (lane == leader) {
-        start = *cell;
-        *cell = start + __popc(peers);
-      }
-      start = __shfl_sync(peers, start, leader);
-      entry[start + rank] = static_cast<uint16_t>((rl << 7) | (c & 127));
-      dest[start + rank] = p;
-    }
-  }
-}
-
 }  // namespace sddmm_tc
 }  // namespace iex
-
-// Layout of a plan (all int32 unless noted): tile_ptr [ntiles + 1] | dest [nnz] | entry uint16
-// [nnz, padded to 4 bytes] | cells [ntiles * 128] (scratch of the build), each part 16-byte aligned.
-namespace {
-struct PlanLayout {
-  size_t tile_ptr, dest, entry, cells, total;
-  int ntiles, T;
-};
-PlanLayout plan_layout(int m, int n, int nnz) {
-  using namespace iex::sddmm_tc;
-  PlanLayout L{};
-  const int bands = (m + TM - 1) / TM;
-  L.T = (n + TN - 1) / TN;
-  L.ntiles = bands * L.T;
-  auto up16 = [](size_t x) { return (x + 15) & ~static_cast<size_t>(15); };
-  L.tile_ptr = 0;
-  L.dest = up16(4 * (static_cast<size_t>(L.ntiles) + 1));
-  L.entry = L.dest + up16(4 * static_cast<size_t>(nnz));
-  L.cells = L.entry + up16(2 * static_cast<size_t>(nnz));
-  L.total = L.cells + up16(4 * static_cast<size_t>(L.ntiles) * TM);
-  return L;
-}
-}  // namespace
-
-extern "C" size_t iex_sddmm_plan_bytes(int m, int n, int nnz) {
-  if (m <= 0 || n <= 0 || nnz < 0) return 0;
-  return plan_layout(m, n, nnz).total;
-}
-
-extern "C" int iex_sddmm_plan_build(int m, int n, int nnz, const int32_t* row_offsets,
-                                    const int32_t* column_indices, void* plan, size_t plan_bytes,
-                                    void* stream) {
-  using namespace iex;
-  using namespace iex::sddmm_tc;
-  if (m < 0 || n < 0 || nnz < 0) return IEX_ERR_BAD_ARG;
-  if (m == 0 || n == 0) return IEX_OK;
-  if (!row_offsets || !plan || (nnz > 0 && !column_indices) || !aligned16(plan)) return IEX_ERR_BAD_ARG;
-  const PlanLayout L = plan_layout(m, n, nnz);
-  if (plan_bytes < L.total) return IEX_ERR_TOO_LARGE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  uint8_t* base = static_cast<uint8_t*>(plan);
-  int* cells = reinterpret_cast<int*>(base + L.cells);
-  cudaError_t e = cudaMemsetAsync(cells, 0, 4 * static_cast<size_t>(L.ntiles) * TM, s);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  const int blocks = (m + 7) / 8;
-  plan_count_kernel<<<blocks, 256, 0, s>>>(m, L.T, row_offsets, column_indices, cells);
-  int st = launch_status();
-  if (st) return st;
-  plan_scan_kernel<<<1, 1024, 0, s>>>(L.ntiles * TM, L.ntiles, cells, reinterpret_cast<int*>(base + L.tile_ptr));
-  st = launch_status();
-  if (st) return st;
-  plan_fill_kernel<<<blocks, 256, 0, s>>>(m, L.T, row_offsets, column_indices, cells,
-                                          reinterpret_cast<uint16_t*>(base + L.entry),
-                                          reinterpret_cast<int*>(base + L.dest));
-  return launch_status();
-}
 
 extern "C" int iex_sddmm_f32_tc_supported(int m, int k, int n, int batch) {
   return (m > 0 && n > 0 && batch == 1 && (k == 32 || k == 64)) ? 1 : 0;
@@ -705,7 +530,7 @@ extern "C" int iex_sddmm_f32_prefers_tc(int m, int k, int n, int nnz, int batch)
   return tiles >= 64 && static_cast<long long>(nnz) * 50 >= static_cast<long long>(m) * n ? 1 : 0;
 }
 
-#ifdef IEX_SDDMM_PROFILE
+#ifdef IEX_TC_PROFILE
 static long long* g_prof_buffer = nullptr;
 extern "C" void iex_sddmm_f32_tc_set_profile_buffer(long long* device_buffer) { g_prof_buffer = device_buffer; }
 #endif
@@ -718,7 +543,7 @@ extern "C" int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, 
   if (m == 0 || nnz == 0) return IEX_OK;
   if (!plan || !lhs || !rhs || !out || !aligned16(plan)) return IEX_ERR_BAD_ARG;
   if (!iex_sddmm_f32_tc_supported(m, k, n, 1) || !aligned16(lhs) || !aligned16(rhs)) return IEX_ERR_UNSUPPORTED;
-  const PlanLayout L = plan_layout(m, n, nnz);
+  const tile_plan::Layout L = tile_plan::layout(m, n, nnz, TN);
   const uint8_t* base = static_cast<const uint8_t*>(plan);
   Params p{};
   p.m = m;
@@ -733,11 +558,11 @@ extern "C" int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, 
   p.out = out;
   p.accumulate = accumulate;
   p.status = tc::status_word();
-#ifdef IEX_SDDMM_PROFILE
+#ifdef IEX_TC_PROFILE
   p.prof = g_prof_buffer;
 #endif
   const int bands = (m + TM - 1) / TM;
-  const int T = L.T;
+  const int T = L.tiles_per_band;
   p.tiles_per_band = T;
   // runs per band: enough to give every SM a unit
   const int sms = tc::sm_count();

@@ -21,6 +21,9 @@ module only loads it.  Operators:
   sddmm_tc_planned(a, b, plan, nnz)                             SDDMM on tensor cores (fp32,
                                                                 TF32 head/tail tiles), a [m, k],
                                                                 b [n, k] -> [nnz]
+  spmm_plan(row_offsets, column_indices, m, k)                  pattern-only plan (build once)
+  spmm_tc_planned(b, values, plan, m)                           SpMM on tensor cores (fp32),
+                                                                A [m, k] x b [k, n] -> [m, n]
 With ``IEX_VALIDATE_CSR=1`` in the environment every sparse operator runs that check on its
 arguments first and raises on a malformed matrix (debugging aid; one extra kernel and a
 synchronisation per call).
@@ -56,4 +59,6 @@ OP_NAMES = (
     "validate_csr",
     "sddmm_plan",
     "sddmm_tc_planned",
+    "spmm_plan",
+    "spmm_tc_planned",
 )

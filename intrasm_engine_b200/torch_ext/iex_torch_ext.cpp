@@ -353,6 +353,43 @@ at::Tensor sddmm_tc_planned(const at::Tensor& a, const at::Tensor& b, const at::
   return out;
 }
 
+// Tile plan of a pattern with 64-column tiles, for spmm_tc_planned (k = A's column count).
+at::Tensor spmm_plan(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t k) {
+  check_common({{"row_offsets", &row_offsets}, {"column_indices", &column_indices}});
+  TORCH_CHECK(row_offsets.scalar_type() == at::kInt && column_indices.scalar_type() == at::kInt,
+              "index tensors must be int32");
+  TORCH_CHECK(row_offsets.dim() == 1 && row_offsets.size(0) == m + 1, "row_offsets must have m + 1 entries");
+  c10::cuda::CUDAGuard guard(row_offsets.device());
+  const int64_t nnz = column_indices.numel();
+  const size_t bytes = iex_tile_plan_bytes(m, k, nnz, 64);
+  at::Tensor plan = at::empty({static_cast<int64_t>(std::max<size_t>(bytes, 16))},
+                              row_offsets.options().dtype(at::kByte));
+  check_status(iex_tile_plan_build(m, k, nnz, 64, row_offsets.data_ptr<int>(), column_indices.data_ptr<int>(),
+                                   plan.data_ptr(), bytes, stream_of(row_offsets)),
+               "iex_tile_plan_build");
+  return plan;
+}
+
+// CSR SpMM on tensor cores with a plan from spmm_plan: A [m, k] (values in storage order) times
+// b [k, n] fp32 -> [m, n]
+at::Tensor spmm_tc_planned(const at::Tensor& b, const at::Tensor& values, const at::Tensor& plan, int64_t m) {
+  TORCH_CHECK(b.dim() == 2 && values.dim() == 1, "b must be [k, n] and values [nnz]");
+  check_common({{"b", &b}, {"values", &values}, {"plan", &plan}});
+  TORCH_CHECK(b.scalar_type() == at::kFloat && values.scalar_type() == at::kFloat, "b and values must be float32");
+  TORCH_CHECK(plan.scalar_type() == at::kByte, "plan must come from spmm_plan");
+  const int64_t k = b.size(0), n = b.size(1), nnz = values.numel();
+  TORCH_CHECK(static_cast<size_t>(plan.numel()) >= iex_tile_plan_bytes(m, k, nnz, 64),
+              "plan was built for another pattern size");
+  c10::cuda::CUDAGuard guard(b.device());
+  at::Tensor out = at::empty({m, n}, b.options());
+  const size_t need = iex_spmm_f32_tc_workspace_bytes(m, k, n);
+  at::Tensor scratch = at::empty({static_cast<int64_t>(std::max<size_t>(need, 16))}, b.options().dtype(at::kByte));
+  check_status(iex_spmm_f32_tc(m, k, n, nnz, plan.data_ptr(), values.data_ptr<float>(), b.data_ptr<float>(),
+                               out.data_ptr<float>(), scratch.data_ptr(), need, stream_of(b)),
+               "iex_spmm_f32_tc");
+  return out;
+}
+
 // 0 when the CSR is well formed, else the OR of the IEX_CSR_* bits (include/iex_b200.h)
 int64_t validate_csr(const at::Tensor& row_offsets, const at::Tensor& column_indices, int64_t m, int64_t k,
                      bool require_ascending) {
@@ -374,6 +411,8 @@ TORCH_LIBRARY(iex_ops, m) {
   m.def("validate_csr(Tensor row_offsets, Tensor column_indices, int m, int k, bool require_ascending) -> int");
   m.def("sddmm_plan(Tensor row_offsets, Tensor column_indices, int m, int n) -> Tensor");
   m.def("sddmm_tc_planned(Tensor a, Tensor b, Tensor plan, int nnz) -> Tensor");
+  m.def("spmm_plan(Tensor row_offsets, Tensor column_indices, int m, int k) -> Tensor");
+  m.def("spmm_tc_planned(Tensor b, Tensor values, Tensor plan, int m) -> Tensor");
 }
 
 // CUDA dispatch key only: a CPU tensor reaches no implementation (there is no CPU path).
@@ -389,4 +428,6 @@ TORCH_LIBRARY_IMPL(iex_ops, CUDA, m) {
   m.impl("validate_csr", &validate_csr);
   m.impl("sddmm_plan", &sddmm_plan);
   m.impl("sddmm_tc_planned", &sddmm_tc_planned);
+  m.impl("spmm_plan", &spmm_plan);
+  m.impl("spmm_tc_planned", &spmm_tc_planned);
 }

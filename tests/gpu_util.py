@@ -140,3 +140,19 @@ def sddmm_close(got, exact, sum_abs):
     if exact.size == 0:
         return got.size == 0
     return bool(np.all(np.abs(got - exact) <= 1e-5 * np.abs(exact) + 2e-6 * np.asarray(sum_abs, np.float64)))
+
+
+def spmm_f32_tc(a: DevCSR, dense2d, values=None):
+    """iex_tile_plan_build (64-column tiles) + iex_spmm_f32_tc: dense [k, n] device fp32 -> [m, n]."""
+    k, n = dense2d.shape
+    nbytes = _lib.lib.iex_tile_plan_bytes(a.m, k, a.nnz, 64)
+    plan = torch.empty(max(int(nbytes), 16), dtype=torch.uint8, device=DEV)
+    _lib.call("iex_tile_plan_build", a.m, k, a.nnz, 64, ptr(a.row_offsets), ptr(a.column_indices), ptr(plan),
+              nbytes, stream_ptr())
+    need = _lib.lib.iex_spmm_f32_tc_workspace_bytes(a.m, k, n)
+    ws = torch.empty(max(int(need), 16), dtype=torch.uint8, device=DEV)
+    out = torch.full((a.m, n), float("nan"), dtype=torch.float32, device=DEV)
+    vals = a.values if values is None else values
+    _lib.call("iex_spmm_f32_tc", a.m, k, n, a.nnz, ptr(plan), ptr(vals), ptr(dense2d), ptr(out), ptr(ws), need,
+              stream_ptr())
+    return out

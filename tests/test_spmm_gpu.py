@@ -250,3 +250,80 @@ def test_torch_ops_spmm(oracle):
                                                            dh.row_offsets, dh.column_indices, 64)
     ref = oracle.spmm(ah.row_indices, ah.values, ah.row_offsets, ah.column_indices, bh, 64)
     np.testing.assert_array_equal(out.cpu().numpy(), ref.astype(np.float16))
+
+
+# ----------------------------------------------------------------------------------------
+# Tensor-core fp32 SpMM (iex_tile_plan_build + iex_spmm_f32_tc): a band of the sparse matrix
+# expanded into TF32 head/tail planes, multiplied with the dense rows on tcgen05.  The bar is
+# the task's 1e-5 relative, measured against the double-precision product and the sum of the
+# terms' magnitudes (the summation order differs from the oracle's); small integers are exact.
+# ----------------------------------------------------------------------------------------
+
+def _check_spmm_tc(oracle, a, b):
+    got = G.spmm_f32_tc(G.DevCSR(a), G.dev(b)).cpu().numpy()
+    torch.cuda.synchronize()
+    assert _lib.lib.iex_last_device_status(1) == 0
+    dense_a = a.to_dense().astype(np.float64)
+    exact = dense_a @ b.astype(np.float64)
+    sabs = np.abs(dense_a) @ np.abs(b.astype(np.float64))
+    assert got.shape == exact.shape and not np.isnan(got).any()
+    assert np.all(np.abs(got - exact) <= 1e-5 * np.abs(exact) + 2e-6 * sabs), \
+        float(np.max(np.abs(got - exact) / (1e-5 * np.abs(exact) + 2e-6 * sabs + 1e-300)))
+    return got
+
+
+@pytest.mark.parametrize("m,k,n,density", [
+    (128, 64, 64, 0.2), (128, 128, 32, 0.5), (1, 1, 32, 1.0), (130, 257, 64, 0.2), (300, 1000, 64, 0.05),
+    (1000, 300, 32, 0.05), (256, 4096, 64, 0.02), (2048, 512, 64, 0.3), (129, 129, 64, 1.0),
+    (640, 640, 64, 0.0), (20000, 256, 32, 0.03),
+])
+def test_spmm_tc_f32_shapes(oracle, m, k, n, density):
+    rng = np.random.default_rng(m + 3 * k + 7 * n)
+    a = syn.csr_from_mask(rng.random((m, k)) < density, rng=rng)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    _check_spmm_tc(oracle, a, b)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_spmm_tc_f32_random_shapes(oracle, seed):
+    rng = np.random.default_rng(1300 + seed)
+    m, k = int(rng.integers(1, 1500)), int(rng.integers(1, 1500))
+    n = int(rng.choice([32, 64]))
+    row_density = rng.choice([0.0, 0.01, 0.05, 0.3, 1.0], size=m, p=[0.1, 0.2, 0.4, 0.2, 0.1])
+    a = syn.csr_from_mask(rng.random((m, k)) < row_density[:, None], rng=rng)
+    b = rng.standard_normal((k, n)).astype(np.float32)
+    _check_spmm_tc(oracle, a, b)
+
+
+def test_spmm_tc_f32_exact_on_small_integers_and_repeatable(oracle):
+    rng = np.random.default_rng(17)
+    m, k, n = 700, 900, 64
+    a = syn.csr_from_mask(rng.random((m, k)) < 0.07, rng=rng)
+    a.values[:] = rng.integers(-7, 8, size=a.nnz).astype(np.float32)
+    b = rng.integers(-7, 8, size=(k, n)).astype(np.float32)
+    da, db = G.DevCSR(a), G.dev(b)
+    got = G.spmm_f32_tc(da, db)
+    ref = oracle.spmm(a.row_indices, a.values, a.row_offsets, a.column_indices, b, m)[0]
+    np.testing.assert_array_equal(got.cpu().numpy(), ref)
+    # a second launch reuses stages whose entries were zeroed again: same bits
+    assert torch.equal(G.spmm_f32_tc(da, db), got)
+
+
+def test_spmm_tc_f32_cfg2_full_size(oracle):
+    """Benchmark configuration 2's follow-on SpMM (scores CSR 4096x4096 at 5 % times V 4096x64)
+    on the tensor-core kernel: against the double-precision product, the CUDA-core kernel and
+    the torch operators."""
+    mask, q, kk, v = syn.sddmm_chain_case(0)
+    rng = np.random.default_rng(5)
+    mask.values[:] = rng.standard_normal(mask.nnz).astype(np.float32)
+    got = _check_spmm_tc(oracle, mask, v)
+    dm = G.DevCSR(mask)
+    simt = G.spmm_f32(dm, G.dev(v)[None])[0].cpu().numpy()
+    assert G.close(got, simt, 1e-5, 1e-5)
+    import intrasm_engine_b200  # noqa: F401
+    ops = torch.ops.iex_ops
+    plan = ops.spmm_plan(dm.row_offsets, dm.column_indices, 4096, 4096)
+    assert torch.equal(ops.spmm_tc_planned(G.dev(v), dm.values, plan, 4096).cpu(), torch.as_tensor(got))
+    assert _lib.lib.iex_spmm_f32_prefers_tc(4096, 4096, 64, mask.nnz) == 0      # 5 %: gather kernels win
+    assert _lib.lib.iex_spmm_f32_prefers_tc(4096, 4096, 64, 3 * mask.nnz) == 1  # 15 %: dense tiles win
+    assert _lib.lib.iex_spmm_f32_tc_supported(4096, 4096, 48) == 0
