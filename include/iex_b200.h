@@ -170,6 +170,20 @@ IEX_API int iex_spmm_f32_prefers_tc(int m, int k, int n, int nnz);
 IEX_API int iex_linear_f16(int tokens, int in_features, int out_features, const void* input,
                            const void* weight, void* out, void* stream);
 
+/* Backward pass of the dense branch on the same tensor-core kernel (operands read in their
+ * other major-ness straight from the forward's tensors, no transposed copies).  Replace the two
+ * cuBLAS calls of MyLinear.backward
+ * (intrasm_engine/pytorch/cpp_extensions/layers_and_funcs/torch.py:20-31).
+ *   dgrad  dinput [tokens, in_features] = grad [tokens, out_features] * weight [out_features, in_features]
+ *          tokens a multiple of 16 and <= 256; in_features, out_features multiples of 8.
+ *   wgrad  dweight [out_features, in_features] = grad^T * input, input [tokens, in_features]
+ *          any number of tokens that is a multiple of 8; in_features, out_features multiples of 8.
+ * All row-major fp16, 16-byte aligned; fp32 accumulation. */
+IEX_API int iex_linear_f16_dgrad(int tokens, int in_features, int out_features, const void* grad,
+                                 const void* weight, void* dinput, void* stream);
+IEX_API int iex_linear_f16_wgrad(int tokens, int in_features, int out_features, const void* grad,
+                                 const void* input, void* dweight, void* stream);
+
 /* CSR SpMM on tensor cores: out[r, :] = sum_p values[p] * dense[col[p], :].
  * Same contract as iex_spmm_f16_i16 / _i32 with batch = 1 and no bias (replaces
  * my_sputnik::CudaSpmm5, extensions.h:30), plus one precondition: column indices ascend

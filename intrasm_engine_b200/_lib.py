@@ -51,6 +51,9 @@ SIGNATURES = {
     "iex_sddmm_f32_prefers_tc": (c_int, [c_int, c_int, c_int, c_int, c_int]),
     # tokens in_features out_features input weight out stream
     "iex_linear_f16": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr]),
+    # tokens in_features out_features grad weight|input dinput|dweight stream
+    "iex_linear_f16_dgrad": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr]),
+    "iex_linear_f16_wgrad": (c_int, [c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr]),
     # m k n nnz row_offsets cols index_bits values dense out stream
     "iex_spmm_f16_tc": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
                                 c_ptr, c_ptr]),

@@ -119,6 +119,8 @@ template <typename IT>
 __global__ void __launch_bounds__(256)
 csr_to_dense_f16_kernel(int m, int k, const int* __restrict__ row_offsets, const IT* __restrict__ cols,
                         const __half* __restrict__ values, __half* __restrict__ out) {
+  grid_dependency_wait();  // `out` may still be read by the kernel before this one
+  grid_launch_dependents();
   for (int r = blockIdx.x; r < m; r += gridDim.x) {
     __half* row = out + static_cast<size_t>(r) * k;
     if ((k & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
@@ -211,15 +213,12 @@ extern "C" int iex_csr_to_dense_f16(int m, int k, const int32_t* row_offsets, co
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = m < 4 * kNumSMs ? m : 4 * kNumSMs;
   if (index_bits == 16)
-    csr_to_dense_f16_kernel<uint16_t><<<grid, 256, 0, s>>>(m, k, row_offsets,
-                                                          static_cast<const uint16_t*>(column_indices),
-                                                          static_cast<const __half*>(values),
-                                                          static_cast<__half*>(out));
-  else
-    csr_to_dense_f16_kernel<int><<<grid, 256, 0, s>>>(m, k, row_offsets, static_cast<const int*>(column_indices),
-                                                      static_cast<const __half*>(values),
-                                                      static_cast<__half*>(out));
-  return launch_status();
+    return launch_overlapped(csr_to_dense_f16_kernel<uint16_t>, dim3(grid), dim3(256), 0, s, m, k, row_offsets,
+                             static_cast<const uint16_t*>(column_indices), static_cast<const __half*>(values),
+                             static_cast<__half*>(out));
+  return launch_overlapped(csr_to_dense_f16_kernel<int>, dim3(grid), dim3(256), 0, s, m, k, row_offsets,
+                           static_cast<const int*>(column_indices), static_cast<const __half*>(values),
+                           static_cast<__half*>(out));
 }
 
 extern "C" int iex_dense_to_csr_count(int m, int k, const void* dense, int value_bits, int relu,

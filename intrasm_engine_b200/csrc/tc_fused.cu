@@ -67,6 +67,11 @@ struct Params {
   __half* d_out_copies[kMaxPeers - 1];
   int d_num_copies;
   int d_b_mn;  // B operand of the dense branch is MN-major ([K, N]) instead of K-major ([N, K])
+  int d_a_mn;  // A operand of the dense branch is MN-major ([K, M]) instead of K-major ([M, K])
+  // Dense units over column blocks: with d_ncols > 0 the B operand is [K, d_ncols] (MN-major),
+  // a unit is (128-row tile, block of n columns), and d_parts = d_nblocks counts the blocks
+  // (no split-K).
+  int d_nblocks, d_ncols;
   // sparse branch: out[r * n + t]
   int s_tiles, s_m, s_nnz;
   int s_tile_rows;  // rows of a sparse tile (a multiple of 8, <= 128; rows above it stay zero)
@@ -105,6 +110,7 @@ __device__ int g_status = 0;  // last device-side failure (IEX_ERR_TIMEOUT) of t
 struct Unit {
   bool sparse;
   int tile, part, parts;
+  int nblock;  // column block of the B operand (dense units over column blocks), else 0
 };
 __device__ __forceinline__ Unit unit_of(int u, const Params& prm, int grid) {
   const int S = prm.s_tiles * prm.s_parts, D = prm.d_tiles * prm.d_parts;
@@ -118,6 +124,12 @@ __device__ __forceinline__ Unit unit_of(int u, const Params& prm, int grid) {
   un.parts = un.sparse ? prm.s_parts : prm.d_parts;
   un.tile = idx / un.parts;
   un.part = idx - un.tile * un.parts;
+  un.nblock = 0;
+  if (!un.sparse && prm.d_ncols > 0) {  // the "parts" of the list are column blocks
+    un.nblock = un.part;
+    un.part = 0;
+    un.parts = 1;
+  }
   return un;
 }
 
@@ -368,6 +380,10 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_generic;
+  // Everything above touched only this CTA's own shared and tensor memory and may overlap the
+  // end of the kernel before this one in the stream; global memory comes next.
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   // Dense stages and sparse slots / rings overlay the same shared memory.  A role that writes
   // shared memory for a unit whose kind differs from the CTA's previous unit first waits until
@@ -423,11 +439,16 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const uint32_t a_dst = smem_base + s * stage_bytes;
             const uint32_t b_dst = a_dst + A_STAGE_BYTES;
             mbar_arrive_expect_tx(full_bar(s), b_stage_bytes + A_STAGE_BYTES);
-            tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, tile * BM);
-            tma_load_2d(a_dst + A_ATOM_BYTES, &tma_a, full_bar(s), kb * BK + 64, tile * BM);
+            if (prm.d_a_mn) {  // A [K, M]: two [128 k-rows x 64 cols] boxes
+              tma_load_2d(a_dst, &tma_a, full_bar(s), tile * BM, kb * BK);
+              tma_load_2d(a_dst + A_ATOM_BYTES, &tma_a, full_bar(s), tile * BM + 64, kb * BK);
+            } else {
+              tma_load_2d(a_dst, &tma_a, full_bar(s), kb * BK, tile * BM);
+              tma_load_2d(a_dst + A_ATOM_BYTES, &tma_a, full_bar(s), kb * BK + 64, tile * BM);
+            }
             if (b_mn) {  // X [K, N]: one [128 k-rows x 64 cols] box per 64 columns
               for (int j = 0; j < n / 64; ++j)
-                tma_load_2d(b_dst + j * (BK * 128), &tma_b_dense, full_bar(s), j * 64, kb * BK);
+                tma_load_2d(b_dst + j * (BK * 128), &tma_b_dense, full_bar(s), un.nblock * n + j * 64, kb * BK);
             } else {  // X^T [N, K]: two [N rows x 64 k] boxes
               tma_load_2d(b_dst, &tma_b_dense, full_bar(s), kb * BK, 0);
               tma_load_2d(b_dst + n * 128, &tma_b_dense, full_bar(s), kb * BK + 64, 0);
@@ -473,8 +494,8 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           }
         } else {
           const int kb0 = un.part * k_blocks / un.parts, kb1 = (un.part + 1) * k_blocks / un.parts;
-          const bool b_mn = prm.d_b_mn;
-          const uint32_t idesc = b_mn ? idesc_mn : idesc_k;
+          const bool b_mn = prm.d_b_mn, a_mn = prm.d_a_mn;
+          const uint32_t idesc = (b_mn ? idesc_mn : idesc_k) | (a_mn ? (1u << 15) : 0u);
           for (int kb = kb0; kb < kb1; ++kb, ++it) {
             const int s = it % S;
             const uint32_t ph = (it / S) & 1u;
@@ -482,20 +503,24 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             tcgen05_fence_after();
             const uint32_t a_base = smem_base + s * stage_bytes;
             const uint32_t b_base = a_base + A_STAGE_BYTES;
-            const uint64_t adesc0 = smem_desc(a_base, 16, 1024);
+            // K-major A: two 64-wide K atoms of 128 rows; MN-major A: two 64-wide M atoms of 128 k-rows
+            const uint64_t adesc0 = a_mn ? smem_desc(a_base, BK * 128, 1024) : smem_desc(a_base, 16, 1024);
+            auto a_step = [&](int ks) {
+              return a_mn ? desc_advance(adesc0, ks * (UMMA_K * 128))
+                          : desc_advance(adesc0, (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32);
+            };
             if (b_mn) {
               const uint64_t bdesc0 = smem_desc(b_base, BK * 128, 1024);
 #pragma unroll
               for (int ks = 0; ks < BK / UMMA_K; ++ks)
-                umma_f16(tmem_base, desc_advance(adesc0, (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32),
-                         desc_advance(bdesc0, ks * (UMMA_K * 128)), idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
+                umma_f16(tmem_base, a_step(ks), desc_advance(bdesc0, ks * (UMMA_K * 128)), idesc,
+                         (kb != kb0 || ks != 0) ? 1u : 0u);
             } else {
               const uint64_t bdesc0 = smem_desc(b_base, 16, 1024);
               const uint32_t b_atom = static_cast<uint32_t>(n) * 128u;  // second 64-wide K atom of B
 #pragma unroll
               for (int ks = 0; ks < BK / UMMA_K; ++ks)
-                umma_f16(tmem_base, desc_advance(adesc0, (ks >> 2) * A_ATOM_BYTES + (ks & 3) * 32),
-                         desc_advance(bdesc0, (ks >> 2) * b_atom + (ks & 3) * 32), idesc,
+                umma_f16(tmem_base, a_step(ks), desc_advance(bdesc0, (ks >> 2) * b_atom + (ks & 3) * 32), idesc,
                          (kb != kb0 || ks != 0) ? 1u : 0u);
             }
             umma_commit(empty_bar(s));
@@ -554,10 +579,14 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(fmaxf(__uint_as_float(r[i]) + bias, 0.f));
           }
           const int copies = sparse ? 0 : prm.d_num_copies;
+          // dense units over column blocks: this unit's columns start at col0, the last block
+          // may be narrower (a multiple of 8 columns)
+          const int col0 = un.nblock * n;
+          const int n_valid = (!sparse && prm.d_ncols > 0) ? min(n, prm.d_ncols - col0) : n;
           for (int pe = 0; pe <= copies; ++pe) {
             __half* o = pe == 0 ? out : prm.d_out_copies[pe - 1];
             if (sn == 1) {
-              uint4* dst = reinterpret_cast<uint4*>(o + row * sm + c0);
+              uint4* dst = reinterpret_cast<uint4*>(o + row * sm + col0 + c0);
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 uint4 pk;
@@ -566,13 +595,13 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 for (int i = 0; i < 4; ++i)
                   h[i] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * i]),
                                            __uint_as_float(r[v * 8 + 2 * i + 1]));
-                dst[v] = pk;
+                if (c0 + v * 8 < n_valid) dst[v] = pk;
               }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i)
-                if (c0 + i < n)  // n need not be a multiple of the 32 columns read at a time
-                  o[row * sm + (c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
+                if (c0 + i < n_valid)  // n need not be a multiple of the 32 columns read at a time
+                  o[row * sm + (col0 + c0 + i) * sn] = __float2half_rn(__uint_as_float(r[i]));
             }
           }
         }
@@ -776,6 +805,8 @@ constexpr int kReduceThreads = 256;
 
 __global__ void __launch_bounds__(kReduceThreads)
 tc_reduce_kernel(const Params prm) {
+  grid_dependency_wait();  // the partial tiles come from the kernel before this one
+  grid_launch_dependents();
   const int n = prm.n;
   const int s_split = prm.s_parts > 1 ? prm.s_tiles : 0;
   const bool sparse = static_cast<int>(blockIdx.x) < s_split;
@@ -851,6 +882,8 @@ constexpr uint32_t kPeerSpinLimit = 1u << 22;  // default limit: a fraction of a
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const PeerSignals ps) {
   __shared__ uint32_t epoch_s;
+  grid_dependency_wait();  // the stores this barrier publishes come from the kernel before it
+  grid_launch_dependents();
   if (threadIdx.x == 0) {
     uint32_t* mine = ps.sig[ps.rank] + ps.world;
     epoch_s = *mine + 1u;
@@ -1010,13 +1043,11 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
   }
   const int units = prm.d_tiles * prm.d_parts + prm.s_tiles * prm.s_parts;
   const int grid = units < sm_count() * ctas_per_sm ? units : sm_count() * ctas_per_sm;
-  kern<<<grid, (kFirstDecodeWarp + ND) * 32, smem, stream>>>(ta, tbd, tbs, prm);
-  int st = launch_status();
-  const int split_tiles = (prm.s_parts > 1 ? prm.s_tiles : 0) + (prm.d_parts > 1 ? prm.d_tiles : 0);
+  int st = launch_overlapped(kern, dim3(grid), dim3((kFirstDecodeWarp + ND) * 32), smem, stream, ta, tbd, tbs, prm);
+  const int split_tiles = (prm.s_parts > 1 ? prm.s_tiles : 0) + (prm.d_parts > 1 && prm.d_ncols == 0 ? prm.d_tiles : 0);
   if (st == 0 && split_tiles > 0) {
     const int slices = (prm.n * (BM / 4) + kReduceThreads - 1) / kReduceThreads;
-    tc_reduce_kernel<<<dim3(split_tiles, slices), kReduceThreads, 0, stream>>>(prm);
-    st = launch_status();
+    st = launch_overlapped(tc_reduce_kernel, dim3(split_tiles, slices), dim3(kReduceThreads), 0, stream, prm);
   }
   return st;
 }
@@ -1214,6 +1245,80 @@ extern "C" int iex_linear_f16_splitk(int tokens, int in_features, int out_featur
                      workspace_bytes, stream);
 }
 
+// The two products of the dense branch's backward pass on the same tensor-core kernel.
+//   dgrad:  dinput [tokens, in] = grad [tokens, out] * weight [out, in]
+//           D[f = in, t] = sum_c W[c, f] * grad[t, c]: A = weight read as [K = out, M = in]
+//           (MN-major), B = grad (K-major, like the forward's input).  tokens <= 256.
+//   wgrad:  dweight [out, in] = grad^T [out, tokens] * input [tokens, in]
+//           D[f = out, j = in] = sum_t grad[t, f] * input[t, j]: A = grad read as [K = tokens,
+//           M = out] (MN-major), B = input [K = tokens, N = in] (MN-major), units over blocks of
+//           256 columns of `in`.  Any number of tokens (K).
+extern "C" int iex_linear_f16_dgrad(int tokens, int in_features, int out_features, const void* grad,
+                                    const void* weight, void* dinput, void* stream) {
+  if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
+  if (tokens == 0 || in_features == 0) return IEX_OK;
+  if (!grad || !weight || !dinput) return IEX_ERR_BAD_ARG;
+  if (tokens % 16 != 0 || tokens > 256 || out_features % 8 != 0 || out_features == 0 || in_features % 8 != 0)
+    return IEX_ERR_UNSUPPORTED;
+  if (!aligned16(grad) || !aligned16(weight)) return IEX_ERR_UNSUPPORTED;
+  CUtensorMap ta, tb;
+  int st = make_map(&ta, weight, out_features, in_features, BK);  // [K rows, M cols], boxes of 128 k-rows
+  if (st) return st;
+  st = make_map(&tb, grad, tokens, out_features, tokens);
+  if (st) return st;
+  Params p{};
+  p.d_tiles = (in_features + BM - 1) / BM;
+  p.d_m = in_features;
+  p.d_out = static_cast<__half*>(dinput);
+  p.d_stride_m = 1;
+  p.d_stride_n = in_features;
+  p.d_a_mn = 1;
+  p.k = out_features;
+  p.n = tokens;
+  p.tmem_cols = tmem_cols_for(tokens);
+  p.status = status_word();
+  st = bind_workspace(p, 1, 1, nullptr, 0);
+  if (st) return st;
+  const int stages = dense_stages(tokens, kMaxStages);
+  if (stages < 2) return IEX_ERR_UNSUPPORTED;
+  return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int iex_linear_f16_wgrad(int tokens, int in_features, int out_features, const void* grad,
+                                    const void* input, void* dweight, void* stream) {
+  if (tokens < 0 || in_features < 0 || out_features < 0) return IEX_ERR_BAD_ARG;
+  if (out_features == 0 || in_features == 0) return IEX_OK;
+  if (!grad || !input || !dweight) return IEX_ERR_BAD_ARG;
+  if (tokens % 8 != 0 || tokens == 0 || out_features % 8 != 0 || in_features % 8 != 0) return IEX_ERR_UNSUPPORTED;
+  if (!aligned16(grad) || !aligned16(input) || !aligned16(dweight)) return IEX_ERR_UNSUPPORTED;
+  const int nblk = in_features >= 256 ? 256 : ((in_features + 63) / 64) * 64;  // columns per unit
+  CUtensorMap ta, tb;
+  int st = make_map(&ta, grad, tokens, out_features, BK);  // [K = tokens rows, M = out cols]
+  if (st) return st;
+  st = make_map(&tb, input, tokens, in_features, BK);  // [K rows, N cols], boxes of 128 k-rows
+  if (st) return st;
+  Params p{};
+  p.d_tiles = (out_features + BM - 1) / BM;
+  p.d_m = out_features;
+  p.d_out = static_cast<__half*>(dweight);
+  p.d_stride_m = in_features;
+  p.d_stride_n = 1;
+  p.d_a_mn = 1;
+  p.d_b_mn = 1;
+  p.d_nblocks = (in_features + nblk - 1) / nblk;
+  p.d_ncols = in_features;
+  p.k = tokens;
+  p.n = nblk;
+  p.tmem_cols = tmem_cols_for(nblk);
+  p.status = status_word();
+  p.s_parts = 1;
+  p.d_parts = p.d_nblocks;  // the unit list counts column blocks where it would count K parts
+  p.partials = nullptr;
+  const int stages = dense_stages(nblk, kMaxStages);
+  if (stages < 2) return IEX_ERR_UNSUPPORTED;
+  return launch_units<0, uint16_t>(ta, tb, tb, p, stages, 1, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int iex_spmm_f16_tc(int m, int k, int n, int nnz, const int32_t* row_offsets,
                                const void* column_indices, int index_bits, const void* values,
                                const void* dense, void* out, void* stream) {
@@ -1359,8 +1464,7 @@ extern "C" int iex_peer_barrier_bounded(void* const* signals, int world, int ran
   ps.rank = rank;
   ps.status = status_word();
   ps.max_polls = max_polls == 0 ? kPeerSpinLimit : (max_polls > kPeerSpinLimit ? kPeerSpinLimit : max_polls);
-  peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(ps);
-  return launch_status();
+  return launch_overlapped(peer_barrier_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), ps);
 }
 
 extern "C" int iex_peer_barrier(void* const* signals, int world, int rank, void* stream) {

@@ -11,6 +11,8 @@ module only loads it.  Operators:
   spmm_sputnik_reuse_weight_half(b, row_indices, values, row_offsets, column_indices, m)
   sddmm_sputnik_atomic_upd_weight(a, b, row_indices, row_offsets, column_indices)
   linear_fp16(input, weight)                                    input @ weight.T
+  linear_fp16_dgrad(grad, weight)                               grad @ weight     (d input)
+  linear_fp16_wgrad(grad, input)                                grad.T @ input    (d weight)
   spmm_tc_half(x, row_offsets, values, column_indices, m)       A_csr @ x on tensor cores
   fused_spmm_linear_half(x, row_offsets, values, column_indices, m, weight)
                                                                 (A_csr @ x, (weight @ x).T)
@@ -53,6 +55,8 @@ OP_NAMES = (
     "spmm_sputnik_reuse_weight_half",
     "sddmm_sputnik_atomic_upd_weight",
     "linear_fp16",
+    "linear_fp16_dgrad",
+    "linear_fp16_wgrad",
     "spmm_tc_half",
     "fused_spmm_linear_half",
     "csr_to_dense_half",

@@ -5,7 +5,9 @@ Same arguments as intrasm_engine/pytorch/cpp_extensions/layers_and_funcs/torch.p
 in_features a multiple of 8 run on the tcgen05 kernel, whatever the token count (blocks of
 up to 256 tokens, a ragged tail padded); other dtypes (the reference's ``MyLinear`` is
 dtype-agnostic, :17) are a plain library GEMM through ``torch.mm``.  The backward pass is
-the reference's two matmuls.
+the reference's two matmuls (:20-31), for fp16 on the same tensor-core kernel
+(``linear_fp16_dgrad`` / ``linear_fp16_wgrad``: the operands are read in their other
+major-ness, no transposed copies), otherwise through ``torch.mm``.
 """
 from __future__ import annotations
 
@@ -61,10 +63,19 @@ class MyLinear(MyAutogradFunc):
         grad_input = grad_weight = None
         with captured(ctx.get("backward_constructor"), ctx.get("stream_beg", 0),
                       ctx.get("constructor_enabled", False)):
-            if need_input:
-                grad_input = grad_output.mm(weight)
-            if need_weight:
-                grad_weight = grad_output.t().mm(input)
+            own = (grad_output.dtype == torch.float16 and grad_output.is_cuda and weight.dtype == torch.float16
+                   and input.dtype == torch.float16 and weight.size(0) % 8 == 0 and weight.size(1) % 8 == 0)
+            if own:  # both products on the tensor-core kernel, operands read as they lie
+                g = grad_output.contiguous()
+                if need_input:
+                    grad_input = torch.ops.iex_ops.linear_fp16_dgrad(g, weight.contiguous())
+                if need_weight:
+                    grad_weight = torch.ops.iex_ops.linear_fp16_wgrad(g, input.contiguous())
+            else:    # other dtypes: the library GEMMs, as in the reference
+                if need_input:
+                    grad_input = grad_output.mm(weight)
+                if need_weight:
+                    grad_weight = grad_output.t().mm(input)
         return grad_input, grad_weight
 
 

@@ -249,6 +249,62 @@ at::Tensor linear_fp16(const at::Tensor& input, const at::Tensor& weight) {
   return out;
 }
 
+// dinput = grad @ weight (blocks of up to 256 tokens, a ragged tail padded with zero rows)
+at::Tensor linear_fp16_dgrad(const at::Tensor& grad, const at::Tensor& weight) {
+  TORCH_CHECK(grad.dim() == 2 && weight.dim() == 2 && grad.size(1) == weight.size(0),
+              "grad must be [tokens, out_features] and weight [out_features, in_features]");
+  check_common({{"grad", &grad}, {"weight", &weight}});
+  TORCH_CHECK(grad.scalar_type() == at::kHalf && weight.scalar_type() == at::kHalf, "grad and weight must be float16");
+  c10::cuda::CUDAGuard guard(grad.device());
+  const int64_t tokens = grad.size(0), out_features = weight.size(0), in_features = weight.size(1);
+  at::Tensor dinput = at::empty({tokens, in_features}, grad.options());
+  if (tokens == 0 || in_features == 0) return dinput;
+  auto block = [&](const at::Tensor& g, at::Tensor d) {
+    check_status(iex_linear_f16_dgrad(g.size(0), in_features, out_features, g.data_ptr(), weight.data_ptr(),
+                                      d.data_ptr(), stream_of(grad)),
+                 "iex_linear_f16_dgrad");
+  };
+  const int64_t whole = tokens / 16 * 16;
+  for (int64_t t0 = 0; t0 < whole; t0 += 256) {
+    const int64_t rows = std::min<int64_t>(256, whole - t0);
+    block(grad.narrow(0, t0, rows), dinput.narrow(0, t0, rows));
+  }
+  if (whole < tokens) {
+    at::Tensor tail_in = at::zeros({16, out_features}, grad.options());
+    tail_in.narrow(0, 0, tokens - whole).copy_(grad.narrow(0, whole, tokens - whole));
+    at::Tensor tail_out = at::empty({16, in_features}, grad.options());
+    block(tail_in, tail_out);
+    dinput.narrow(0, whole, tokens - whole).copy_(tail_out.narrow(0, 0, tokens - whole));
+  }
+  return dinput;
+}
+
+// dweight = grad^T @ input (the token dimension is the contraction; padded to a multiple of 8)
+at::Tensor linear_fp16_wgrad(const at::Tensor& grad, const at::Tensor& input) {
+  TORCH_CHECK(grad.dim() == 2 && input.dim() == 2 && grad.size(0) == input.size(0),
+              "grad must be [tokens, out_features] and input [tokens, in_features]");
+  check_common({{"grad", &grad}, {"input", &input}});
+  TORCH_CHECK(grad.scalar_type() == at::kHalf && input.scalar_type() == at::kHalf, "grad and input must be float16");
+  c10::cuda::CUDAGuard guard(grad.device());
+  const int64_t tokens = grad.size(0), out_features = grad.size(1), in_features = input.size(1);
+  at::Tensor dweight = at::empty({out_features, in_features}, grad.options());
+  if (out_features == 0 || in_features == 0) return dweight;
+  at::Tensor g = grad, x = input;
+  if (tokens % 8 != 0 || tokens == 0) {
+    const int64_t padded = std::max<int64_t>(8, (tokens + 7) / 8 * 8);
+    g = at::zeros({padded, out_features}, grad.options());
+    x = at::zeros({padded, in_features}, input.options());
+    if (tokens > 0) {
+      g.narrow(0, 0, tokens).copy_(grad);
+      x.narrow(0, 0, tokens).copy_(input);
+    }
+  }
+  check_status(iex_linear_f16_wgrad(g.size(0), in_features, out_features, g.data_ptr(), x.data_ptr(),
+                                    dweight.data_ptr(), stream_of(grad)),
+               "iex_linear_f16_wgrad");
+  return dweight;
+}
+
 int tc_sparse_checks(const at::Tensor& x, const at::Tensor& row_offsets, const at::Tensor& values,
                      const at::Tensor& column_indices, int64_t m) {
   TORCH_CHECK(x.dim() == 2, "x must be [k, n]");
@@ -405,6 +461,8 @@ TORCH_LIBRARY(iex_ops, m) {
   m.def("spmm_sputnik_reuse_weight_half(Tensor b, Tensor row_indices, Tensor values, Tensor row_offsets, Tensor column_indices, int m) -> Tensor");
   m.def("sddmm_sputnik_atomic_upd_weight(Tensor a, Tensor b, Tensor row_indices, Tensor row_offsets, Tensor column_indices) -> Tensor");
   m.def("linear_fp16(Tensor input, Tensor weight) -> Tensor");
+  m.def("linear_fp16_dgrad(Tensor grad, Tensor weight) -> Tensor");
+  m.def("linear_fp16_wgrad(Tensor grad, Tensor input) -> Tensor");
   m.def("spmm_tc_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, int m) -> Tensor");
   m.def("fused_spmm_linear_half(Tensor x, Tensor row_offsets, Tensor values, Tensor column_indices, int m, Tensor weight) -> (Tensor, Tensor)");
   m.def("csr_to_dense_half(Tensor row_offsets, Tensor values, Tensor column_indices, int m, int k) -> Tensor");
@@ -422,6 +480,8 @@ TORCH_LIBRARY_IMPL(iex_ops, CUDA, m) {
   m.impl("spmm_sputnik_reuse_weight_half", &spmm_sputnik_reuse_weight_half);
   m.impl("sddmm_sputnik_atomic_upd_weight", &sddmm_sputnik_atomic_upd_weight);
   m.impl("linear_fp16", &linear_fp16);
+  m.impl("linear_fp16_dgrad", &linear_fp16_dgrad);
+  m.impl("linear_fp16_wgrad", &linear_fp16_wgrad);
   m.impl("spmm_tc_half", &spmm_tc_half);
   m.impl("fused_spmm_linear_half", &fused_spmm_linear_half);
   m.impl("csr_to_dense_half", &csr_to_dense_half);

@@ -494,3 +494,45 @@ def test_fused_exact_on_small_integers_cfg4_shape(oracle):
     np.testing.assert_array_equal(out_s.cpu().numpy(), ref_s.astype(np.float16))
     np.testing.assert_array_equal(out_d.cpu().numpy(), ref_d.astype(np.float16))
     _status_clean()
+
+
+# ----------------------------------------------------------------------------------------
+# Backward of the dense branch: dgrad = grad @ W and wgrad = grad^T @ X on the tensor-core
+# kernel (A operand MN-major; wgrad also B MN-major over blocks of 256 columns)
+# ----------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("tokens,cin,cout", [(64, 256, 384), (16, 8, 8), (256, 1024, 1000), (128, 4096, 512),
+                                             (48, 520, 200), (64, 4096, 12288), (256, 200, 136)])
+def test_linear_dgrad_wgrad(tokens, cin, cout):
+    rng = np.random.default_rng(tokens + cin + cout)
+    x = rng.standard_normal((tokens, cin)).astype(np.float16)
+    w = (rng.standard_normal((cout, cin)) * 0.05).astype(np.float16)
+    g = rng.standard_normal((tokens, cout)).astype(np.float16)
+    dx, dw = G.dev(x), G.dev(w)
+    dg = G.dev(g)
+    dinput = torch.full((tokens, cin), 9.0, dtype=torch.float16, device=G.DEV)
+    dweight = torch.full((cout, cin), 9.0, dtype=torch.float16, device=G.DEV)
+    _lib.call("iex_linear_f16_dgrad", tokens, cin, cout, dg.data_ptr(), dw.data_ptr(), dinput.data_ptr(), G.stream_ptr())
+    _lib.call("iex_linear_f16_wgrad", tokens, cin, cout, dg.data_ptr(), dx.data_ptr(), dweight.data_ptr(), G.stream_ptr())
+    ref_i, sabs_i = G.linear_ref_and_sum_abs(g, w.T)
+    ref_w, sabs_w = G.linear_ref_and_sum_abs(g.T, x.T)
+    assert G.tc_close(dinput.cpu().numpy(), ref_i, sabs_i)
+    assert G.tc_close(dweight.cpu().numpy(), ref_w, sabs_w)
+    _status_clean()
+
+
+def test_linear_backward_exact_on_small_integers_and_ops():
+    rng = np.random.default_rng(77)
+    tokens, cin, cout = 72 + 256, 520, 392      # ragged token count through the operators
+    x = rng.integers(-2, 3, size=(tokens, cin)).astype(np.float16)
+    w = rng.integers(-2, 3, size=(cout, cin)).astype(np.float16)
+    g = rng.integers(-2, 3, size=(tokens, cout)).astype(np.float16)
+    ops = torch.ops.iex_ops
+    di = ops.linear_fp16_dgrad(G.dev(g), G.dev(w)).cpu().numpy()
+    dw = ops.linear_fp16_wgrad(G.dev(g), G.dev(x)).cpu().numpy()
+    ref_i = g.astype(np.float32) @ w.astype(np.float32)
+    ref_w = g.astype(np.float32).T @ x.astype(np.float32)
+    assert max(np.abs(ref_i).max(), np.abs(ref_w).max()) < 2048
+    np.testing.assert_array_equal(di, ref_i.astype(np.float16))
+    np.testing.assert_array_equal(dw, ref_w.astype(np.float16))
+    _status_clean()
