@@ -43,7 +43,8 @@ UNIT = "GFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of each kernel on this workload, from
 # one ncu capture per kernel (12 rotating instances; part of an instance is still L2-resident
 # from the kernel before it, hence below the algorithmic bytes)
-NCU_DRAM_BYTES_PER_LAUNCH = {"sddmm_rowtile_kernel": 5.50e6, "spmm_rowgroup_kernel": 7.81e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"sddmm_rowtile_kernel": 5.50e6, "spmm_rowgroup_kernel": 7.81e6,
+                             "sddmm_tc_kernel": 7.19e6}
 
 
 def measured_peak_gbs():

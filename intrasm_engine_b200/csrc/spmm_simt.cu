@@ -1,8 +1,8 @@
 // CSR SpMM on CUDA cores (sm_100a): out[z, r, :] = sum_p values[p] * dense[z, col[p], :].
 //
-// Used for fp32 (where tensor cores would need tf32 splitting) and for fp16 at high
-// sparsity or small shapes.  The moderate-sparsity fp16 case has a tensor-core kernel of
-// its own (spmm_tc.cu).
+// The default for fp32 (spmm_tc.cu holds a TF32 head/tail tensor-core kernel that wins at
+// densities of about 10 % and above) and for fp16 at high sparsity or small shapes; the
+// moderate-sparsity fp16 case runs on the tensor-core kernel in tc_fused.cu.
 //
 // Work decomposition
 //   * One sub-warp ("row group") of LPR lanes owns one row of A and one tile of
