@@ -96,6 +96,13 @@ IEX_API int iex_sddmm_f32(int m, int k, int n, int nnz, const int32_t* row_indic
                   const float* lhs, const float* rhs, float* out, int batch,
                   int accumulate, void* stream);
 
+/* The fp16 instantiation (fp16 operands and result, fp32 accumulation; 16- or 32-bit column
+ * indices), which the reference declares and leaves commented out
+ * (sputnik_kernels.cpp:185-187): the backward pass of an fp16 SpMM needs it.  Overwrites out. */
+IEX_API int iex_sddmm_f16(int m, int k, int n, int nnz, const int32_t* row_indices,
+                  const int32_t* row_offsets, const void* column_indices, int index_bits,
+                  const void* lhs, const void* rhs, void* out, int batch, void* stream);
+
 /* SDDMM on tensor cores (tcgen05.mma.kind::tf32 into TMEM), fp32 in and out; same result
  * contract as iex_sddmm_f32 with batch = 1 (replaces my_sputnik::CudaSddmm2,
  * extensions.h:19-26, :31).  The dense product of a 128-row band of lhs with 128 rows of

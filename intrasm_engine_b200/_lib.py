@@ -32,6 +32,9 @@ SIGNATURES = {
     # m k n nnz row_indices row_offsets cols lhs rhs out batch accumulate stream
     "iex_sddmm_f32": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                               c_ptr, c_int, c_int, c_ptr]),
+    # m k n nnz row_indices row_offsets cols index_bits lhs rhs out batch stream
+    "iex_sddmm_f16": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
+                              c_ptr, c_int, c_ptr]),
     # m n nnz
     "iex_sddmm_plan_bytes": (c_size, [c_int, c_int, c_int]),
     # m n nnz row_offsets cols plan plan_bytes stream

@@ -54,6 +54,7 @@ OP_NAMES = (
     "spmm_sputnik_atomic",
     "spmm_sputnik_reuse_weight_half",
     "sddmm_sputnik_atomic_upd_weight",
+    "sddmm_sputnik_half",
     "linear_fp16",
     "linear_fp16_dgrad",
     "linear_fp16_wgrad",

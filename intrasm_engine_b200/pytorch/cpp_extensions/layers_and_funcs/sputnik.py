@@ -32,10 +32,11 @@ def _spmm(b2d, row_indices, values, row_offsets, column_indices, m, use_tc=False
 
 
 def _sddmm(grad2d, b2d, row_indices, row_offsets, column_indices):
-    out = torch.ops.iex_ops.sddmm_sputnik_atomic_upd_weight(
-        grad2d.float().unsqueeze(0), b2d.float().unsqueeze(0), row_indices, row_offsets,
-        column_indices.to(torch.int32))
-    return out.to(grad2d.dtype)
+    if grad2d.dtype == torch.float16:  # fp16 operands as they are: fp32 accumulation, fp16 result
+        return torch.ops.iex_ops.sddmm_sputnik_half(grad2d.unsqueeze(0), b2d.to(torch.float16).unsqueeze(0),
+                                                    row_indices, row_offsets, column_indices)
+    return torch.ops.iex_ops.sddmm_sputnik_atomic_upd_weight(
+        grad2d.unsqueeze(0), b2d.unsqueeze(0), row_indices, row_offsets, column_indices.to(torch.int32))
 
 
 class MySpMM(MyAutogradFunc):

@@ -197,6 +197,33 @@ at::Tensor sddmm_sputnik_atomic_upd_weight(const at::Tensor& a, const at::Tensor
   return out;
 }
 
+// fp16 SDDMM (the instantiation the reference leaves commented out, sputnik_kernels.cpp:185-187):
+// a [batch, m, k] and b [batch, n, k] fp16 -> fp16 [nnz]; int16 or int32 column indices
+at::Tensor sddmm_sputnik_half(const at::Tensor& a, const at::Tensor& b, const at::Tensor& row_indices,
+                              const at::Tensor& row_offsets, const at::Tensor& column_indices) {
+  TORCH_CHECK(a.dim() == b.dim() && a.dim() == 3, "a and b must be [batch, rows, k]");
+  TORCH_CHECK(a.size(0) == b.size(0) && a.size(2) == b.size(2), "a and b disagree on batch size or k");
+  check_common({{"a", &a}, {"b", &b}, {"row_indices", &row_indices}, {"row_offsets", &row_offsets},
+                {"column_indices", &column_indices}});
+  TORCH_CHECK(a.scalar_type() == at::kHalf && b.scalar_type() == at::kHalf, "a and b must be float16");
+  TORCH_CHECK(row_indices.scalar_type() == at::kInt && row_offsets.scalar_type() == at::kInt,
+              "row_indices and row_offsets must be int32");
+  const bool i16 = column_indices.scalar_type() == at::kShort;
+  TORCH_CHECK(i16 || column_indices.scalar_type() == at::kInt, "column_indices must be int16 or int32");
+  const int batch = a.size(0), m = a.size(1), k = a.size(2), n = b.size(1);
+  TORCH_CHECK(row_indices.size(0) == m && row_offsets.size(0) == m + 1,
+              "row_indices must have m entries and row_offsets m + 1");
+  const int nnz = column_indices.size(0);
+  c10::cuda::CUDAGuard guard(a.device());
+  maybe_validate(row_offsets, column_indices, m, n, &row_indices, false);
+  at::Tensor out = at::empty({nnz}, a.options());
+  check_status(iex_sddmm_f16(m, k, n, nnz, row_indices.data_ptr<int>(), row_offsets.data_ptr<int>(),
+                             column_indices.data_ptr(), i16 ? 16 : 32, a.data_ptr(), b.data_ptr(),
+                             out.data_ptr(), batch, stream_of(a)),
+               "iex_sddmm_f16");
+  return out;
+}
+
 // One block of at most 256 tokens (a multiple of 16) of the dense branch into `out` (a
 // contiguous [tokens, out_features] block).
 void linear_block(const at::Tensor& input, const at::Tensor& weight, at::Tensor out) {
@@ -460,6 +487,7 @@ TORCH_LIBRARY(iex_ops, m) {
   m.def("spmm_sputnik_reuse_weight(Tensor b, Tensor row_indices, Tensor values, Tensor row_offsets, Tensor column_indices, int m) -> Tensor");
   m.def("spmm_sputnik_reuse_weight_half(Tensor b, Tensor row_indices, Tensor values, Tensor row_offsets, Tensor column_indices, int m) -> Tensor");
   m.def("sddmm_sputnik_atomic_upd_weight(Tensor a, Tensor b, Tensor row_indices, Tensor row_offsets, Tensor column_indices) -> Tensor");
+  m.def("sddmm_sputnik_half(Tensor a, Tensor b, Tensor row_indices, Tensor row_offsets, Tensor column_indices) -> Tensor");
   m.def("linear_fp16(Tensor input, Tensor weight) -> Tensor");
   m.def("linear_fp16_dgrad(Tensor grad, Tensor weight) -> Tensor");
   m.def("linear_fp16_wgrad(Tensor grad, Tensor input) -> Tensor");
@@ -479,6 +507,7 @@ TORCH_LIBRARY_IMPL(iex_ops, CUDA, m) {
   m.impl("spmm_sputnik_reuse_weight", &spmm_sputnik_reuse_weight);
   m.impl("spmm_sputnik_reuse_weight_half", &spmm_sputnik_reuse_weight_half);
   m.impl("sddmm_sputnik_atomic_upd_weight", &sddmm_sputnik_atomic_upd_weight);
+  m.impl("sddmm_sputnik_half", &sddmm_sputnik_half);
   m.impl("linear_fp16", &linear_fp16);
   m.impl("linear_fp16_dgrad", &linear_fp16_dgrad);
   m.impl("linear_fp16_wgrad", &linear_fp16_wgrad);

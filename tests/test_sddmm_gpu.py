@@ -252,3 +252,82 @@ def test_sddmm_tc_takes_unsorted_columns_and_rejects_unsupported(oracle):
     assert _lib.lib.iex_sddmm_f32_tc_supported(256, 64, 512, 2) == 0
     assert _lib.lib.iex_sddmm_f32_prefers_tc(4096, 64, 4096, 838861, 1) == 1
     assert _lib.lib.iex_sddmm_f32_prefers_tc(4096, 64, 4096, 20000, 1) == 0
+
+
+# ----------------------------------------------------------------------------- fp16
+def _sddmm_f16(mask, lhs, rhs):
+    from intrasm_engine_b200 import _lib
+    batch, m, k = lhs.shape
+    n = rhs.shape[1]
+    out = torch.empty((mask.nnz,), dtype=torch.float16, device=G.DEV)
+    bits = 16 if mask.column_indices.dtype == torch.int16 else 32
+    _lib.call("iex_sddmm_f16", m, k, n, mask.nnz, G.ptr(mask.row_indices), G.ptr(mask.row_offsets),
+              G.ptr(mask.column_indices), bits, G.ptr(lhs), G.ptr(rhs), G.ptr(out), batch, G.stream_ptr())
+    return out
+
+
+def _f16_bar(got, exact, sum_abs):
+    """fp16 operands, fp32 accumulation, one rounding to fp16 at the end: the bar of the
+    tensor-core fp16 kernels (2^-10 relative for the final rounding + 1e-5 of the sum of the
+    terms' magnitudes for the accumulation order)."""
+    return G.tc_close(got, exact, sum_abs)
+
+
+@pytest.mark.parametrize("m,n,k,density,batch,idx", [
+    (1, 1, 1, 1.0, 1, np.int32), (9, 11, 3, 0.5, 1, np.int16), (64, 64, 8, 0.3, 1, np.int16),
+    (70, 90, 16, 0.2, 2, np.int32), (128, 128, 32, 0.1, 1, np.int16), (100, 300, 36, 0.2, 1, np.int32),
+    (256, 256, 64, 0.05, 3, np.int16), (60, 500, 104, 0.3, 1, np.int16), (64, 64, 128, 0.5, 1, np.int32),
+    (48, 80, 264, 0.2, 2, np.int16), (33, 47, 7, 0.6, 1, np.int32), (128, 64, 64, 0.0, 1, np.int16),
+    (16, 2000, 64, 0.4, 1, np.int16), (512, 512, 256, 0.1, 1, np.int16),
+])
+def test_sddmm_half_shapes(oracle, m, n, k, density, batch, idx):
+    rng = np.random.default_rng(m + 3 * n + 7 * k)
+    mask = syn.csr_from_mask(rng.random((m, n)) < density, rng=rng, index_dtype=idx)
+    lhs = rng.standard_normal((batch, m, k)).astype(np.float16)
+    rhs = rng.standard_normal((batch, n, k)).astype(np.float16)
+    got = _sddmm_f16(G.DevCSR(mask), G.dev(lhs), G.dev(rhs)).cpu().numpy()
+    ci = mask.column_indices.astype(np.int32)
+    exact = oracle.sddmm(lhs.astype(np.float32), rhs.astype(np.float32), mask.row_indices, mask.row_offsets, ci,
+                         f64=True)
+    sabs = oracle.sddmm(np.abs(lhs).astype(np.float32), np.abs(rhs).astype(np.float32), mask.row_indices,
+                        mask.row_offsets, ci, f64=True)
+    assert got.shape == exact.shape
+    assert _f16_bar(got, exact, sabs)
+
+
+def test_sddmm_half_exact_on_small_integers(oracle):
+    """Small-integer operands: every product and partial sum is exact, so is the fp16 result."""
+    rng = np.random.default_rng(4)
+    m, n, k = 300, 700, 64
+    mask = syn.csr_from_mask(rng.random((m, n)) < 0.1, rng=rng, index_dtype=np.int16)
+    lhs = rng.integers(-3, 4, size=(1, m, k)).astype(np.float16)
+    rhs = rng.integers(-3, 4, size=(1, n, k)).astype(np.float16)
+    got = _sddmm_f16(G.DevCSR(mask), G.dev(lhs), G.dev(rhs)).cpu().numpy().astype(np.float64)
+    exact = oracle.sddmm(lhs.astype(np.float32), rhs.astype(np.float32), mask.row_indices, mask.row_offsets,
+                         mask.column_indices.astype(np.int32), f64=True)
+    assert np.array_equal(got, exact)
+
+
+def test_sddmm_half_torch_op_and_fp16_backward(oracle):
+    """The op, and MySpMM's fp16 backward through it: d values = SDDMM(grad, b) without an fp32 detour."""
+    from intrasm_engine_b200.pytorch.cpp_extensions.layers_and_funcs.sputnik import MySpMM
+    from intrasm_engine_b200.pytorch.utils import get_transpose_info
+    rng = np.random.default_rng(6)
+    m, k, n = 256, 384, 64
+    a = syn.csr_from_mask(rng.random((m, k)) < 0.2, rng=rng, std=0.1, dtype=np.float16, index_dtype=np.int16)
+    da = G.DevCSR(a)
+    b = torch.tensor(rng.standard_normal((k, n)).astype(np.float16), device=G.DEV, requires_grad=True)
+    values = da.values.clone().requires_grad_(True)
+    info = get_transpose_info(m, k, da.row_indices, da.row_offsets, da.column_indices)
+    out = MySpMM.run(b, da.row_indices, values, da.row_offsets, da.column_indices, m, info)
+    grad = torch.tensor(rng.standard_normal((m, n)).astype(np.float16), device=G.DEV)
+    out.backward(grad)
+    assert values.grad.dtype == torch.float16
+    g32, b32 = grad.float().cpu().numpy()[None], b.detach().float().cpu().numpy()[None]
+    ci = a.column_indices.astype(np.int32)
+    exact = oracle.sddmm(g32, b32, a.row_indices, a.row_offsets, ci, f64=True)
+    sabs = oracle.sddmm(np.abs(g32), np.abs(b32), a.row_indices, a.row_offsets, ci, f64=True)
+    assert _f16_bar(values.grad.cpu().numpy(), exact, sabs)
+    direct = torch.ops.iex_ops.sddmm_sputnik_half(grad[None], b.detach()[None], da.row_indices, da.row_offsets,
+                                                  da.column_indices)
+    assert torch.equal(direct, values.grad)
