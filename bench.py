@@ -1019,7 +1019,18 @@ def profile_kernel(which: str) -> None:
     def up(z):
         return torch.as_tensor(np.ascontiguousarray(z)).to(dev)
 
-    if which in ("sddmm", "spmm", "sddmm_tc"):
+    if which == "ffn":
+        # config 5 on one GPU: four layers (two weight copies rotating: 2 x 90 MB > L2) through
+        # the product module, i.e. CSR -> dense, the split-K linear and its reduction per layer
+        from intrasm_engine_b200.pytorch.ffn import ReluSparseDownProj
+        tokens, k, n = 256, 11008, 4096
+        act, w = syn.relu_ffn_layer_case(0, 0, tokens, k, n)
+        layer = ReluSparseDownProj(tokens, k, n, device=dev, gather="none")
+        va, ro, ci = up(act.values), up(act.row_offsets), up(act.column_indices)
+        ws = [up(np.ascontiguousarray(w.T)) for _ in range(2)]
+        for i in range(4):
+            layer(va, ro, ci, ws[i % 2])
+    elif which in ("sddmm", "spmm", "sddmm_tc"):
         runs = []
         for i in range(12):  # 12 x 11 MB > L2
             mask, q, k, v = syn.sddmm_chain_case(i, M, N_COLS, K_DIM, DENSITY)
@@ -1068,7 +1079,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-kernel", default=None,
-                    choices=["sddmm", "sddmm_tc", "spmm", "linear", "spmm_tc", "fused"],
+                    choices=["sddmm", "sddmm_tc", "spmm", "linear", "spmm_tc", "fused", "ffn"],
                     help="run a few launches of one kernel on its benchmark workload and exit")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the sections beside the primary workload (used for profiler captures)")
