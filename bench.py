@@ -151,8 +151,8 @@ def flops_of(inst) -> int:
 
 def emit(line: dict, details: dict | None = None) -> None:
     """Prints the ONE JSON line (compact separators, floats to 5 significant digits) and puts
-    the long tables next to it: on stderr and, where that folder exists, in
-    gpurun_out/bench_details.json."""
+    the long tables next to it: on stderr and, where the scratch output folder beside this file
+    exists, in bench_details.json there."""
     def trim(o):
         if isinstance(o, float):
             return float("%.5g" % o)
