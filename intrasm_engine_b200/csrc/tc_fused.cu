@@ -39,6 +39,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tc_prof.cuh"
 #include "tc_ptx.cuh"
 
 namespace iex {
@@ -80,6 +81,7 @@ struct Params {
   const void* s_cols;
   const __half* s_values;
   const float* s_bias;  // optional: out = relu(sum + bias[row]) for the sparse branch
+  IEX_PROF_FIELD
   // shared
   int k, n;
   int num_stages, tmem_cols;
@@ -90,6 +92,9 @@ struct Params {
   int s_a_slots, s_b_slots;
   int s_ring_rows;      // rows the rings are laid out for (>= s_tile_rows)
   uint32_t s_ring_offset, bar_offset;
+  // dense units with a tokens-major output: 16 KB where the epilogue warps turn their rows of
+  // the tile into 16-byte runs along the output's contiguous dimension (0: not available)
+  uint32_t epi_offset;
   // split-K: every tile's K range is cut into `parts` equal runs of k-blocks, one unit
   // each.  With parts > 1 a unit writes its fp32 partial tile to `partials`
   // ([tile][part][128][n], sparse tiles first) and a second, tiny kernel adds the parts in
@@ -310,6 +315,7 @@ __global__ void __launch_bounds__((kFirstDecodeWarp + ND) * 32, 1)
 tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b_dense,
                 const __grid_constant__ CUtensorMap tma_b_sparse, const Params prm) {
   extern __shared__ uint8_t smem_raw[];
+  IEX_PROF_STAMP(threadIdx.x == 0, 42)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int n = prm.n;
   // dense units: ring of S stages, each [A 128x128 | B 128xN]
@@ -380,10 +386,12 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_ptr_generic;
+  IEX_PROF_STAMP(threadIdx.x == 0, 43)
   // Everything above touched only this CTA's own shared and tensor memory and may overlap the
   // end of the kernel before this one in the stream; global memory comes next.
   grid_dependency_wait();
   grid_launch_dependents();
+  IEX_PROF_STAMP(threadIdx.x == 0, 45)
 
   // Dense stages and sparse slots / rings overlay the same shared memory.  A role that writes
   // shared memory for a unit whose kind differs from the CTA's previous unit first waits until
@@ -500,6 +508,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const int s = it % S;
             const uint32_t ph = (it / S) & 1u;
             if (!mbar_wait(full_bar(s), ph, abort_flag, prm.status, 32)) { ok = false; break; }
+            IEX_PROF_STAMP(it == 0, 46)
             tcgen05_fence_after();
             const uint32_t a_base = smem_base + s * stage_bytes;
             const uint32_t b_base = a_base + A_STAGE_BYTES;
@@ -527,6 +536,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           }
         }
         if (ok) umma_commit(accum_full);
+        IEX_PROF_STAMP(true, 47)
       }
     }
   } else if (warp < kFirstDecodeWarp) {
@@ -539,6 +549,7 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const bool sparse = un.sparse;
       const int tile = un.tile;
       if (!mbar_wait(accum_full, unit_it & 1u, abort_flag, prm.status, 256)) { ok = false; break; }
+      IEX_PROF_STAMP(warp == 2 && lane == 0, 48)
       tcgen05_fence_after();
       if (warp == 2 && lane == 0) {
         __threadfence_block();
@@ -556,6 +567,8 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           : prm.partials + (static_cast<size_t>(sparse ? tile * prm.s_parts
                                                         : prm.s_tiles * prm.s_parts + tile * prm.d_parts)) *
                                (static_cast<size_t>(BM) * n);
+      // final (not partial) dense tiles whose output runs along the rows take the staged path
+      const bool staged = !sparse && un.parts == 1 && prm.epi_offset != 0u;
       for (int c0 = 0; c0 < n; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, r);
@@ -565,7 +578,37 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           __syncwarp();
           if (lane == 0) mbar_arrive(accum_empty);
         }
-        if (un.parts > 1) {
+        if (staged) {
+          // Tokens-major output: column c of the tile is a run of 128 rows in memory.  Each warp
+          // turns its 32 rows x 32 columns into 16-byte pieces (8 rows of one column) through
+          // its own 2 KB of shared memory and stores those: 4 vector stores per lane instead of
+          // 32 two-byte ones.  Only lanes of the warp meet, so no barrier beyond __syncwarp.
+          const uint32_t mine = smem_base + prm.epi_offset + static_cast<uint32_t>(q) * 2048u;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint16_t h = __half_as_ushort(__float2half_rn(__uint_as_float(r[i])));
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(mine + i * 64 + lane * 2), "h"(h) : "memory");
+          }
+          __syncwarp();
+          const int row0 = tile * BM + q * 32;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int v = lane + 32 * j;         // piece v: column v >> 2 of the chunk, rows 8 * (v & 3) ..
+            const int col = v >> 2, piece = v & 3;
+            uint4 pk;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(pk.x), "=r"(pk.y), "=r"(pk.z), "=r"(pk.w)
+                         : "r"(mine + col * 64 + piece * 16)
+                         : "memory");
+            const int rr = row0 + piece * 8;
+            if (rr < prm.d_m && c0 + col < n) {
+              const long long off = static_cast<long long>(c0 + col) * prm.d_stride_n + rr;
+              *reinterpret_cast<uint4*>(prm.d_out + off) = pk;
+              for (int pe = 0; pe < prm.d_num_copies; ++pe) *reinterpret_cast<uint4*>(prm.d_out_copies[pe] + off) = pk;
+            }
+          }
+          __syncwarp();  // the pieces are read before the next chunk overwrites them
+        } else if (un.parts > 1) {
           // partial tile stored column-major ([n][128]): the 32 lanes of a warp hold 32
           // consecutive rows, so every store below is one coalesced 128-byte line
           float* dst = part_base + static_cast<size_t>(un.part) * BM * n + static_cast<size_t>(c0) * BM +
@@ -787,8 +830,10 @@ tc_units_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   }
 
   // ---------------------------------------------------------------------- teardown
+  IEX_PROF_STAMP(warp == 2 && lane == 0, 49)
   tcgen05_fence_before();
   __syncthreads();
+  IEX_PROF_STAMP(threadIdx.x == 0, 44)
   if (warp == 1) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
@@ -1025,6 +1070,16 @@ int launch_units(const CUtensorMap& ta, const CUtensorMap& tbd, const CUtensorMa
     data = sparse > data ? sparse : data;
   }
   data = (data + 15) & ~static_cast<size_t>(15);
+  // 8 KB behind everything for the staged epilogue of dense tiles whose output is tokens-major
+  // (contiguous along the tile's rows) and 16-byte friendly; otherwise two-byte stores
+  prm.epi_offset = 0;
+  bool vec_ok = prm.d_tiles > 0 && prm.d_stride_m == 1 && prm.d_ncols == 0 && prm.d_stride_n % 8 == 0 &&
+                prm.d_m % 8 == 0 && aligned16(prm.d_out);
+  for (int i = 0; i < prm.d_num_copies; ++i) vec_ok = vec_ok && aligned16(prm.d_out_copies[i]);
+  if (vec_ok && data + 8192 <= static_cast<size_t>(kDataBudget)) {
+    prm.epi_offset = static_cast<uint32_t>(data);
+    data += 8192;
+  }
   if (stages > kMaxStages || data > static_cast<size_t>(kDataBudget)) return IEX_ERR_UNSUPPORTED;
   prm.bar_offset = static_cast<uint32_t>(data);
   const size_t smem = 1024 + data + kBarBytes;
@@ -1078,6 +1133,11 @@ extern "C" int iex_last_device_status(int clear) {
   }
   return v;
 }
+
+#ifdef IEX_TC_PROFILE
+static long long* g_tc_prof_buffer = nullptr;
+extern "C" void iex_tc_set_profile_buffer(long long* device_buffer) { g_tc_prof_buffer = device_buffer; }
+#endif
 
 namespace {
 
@@ -1159,6 +1219,9 @@ int linear_impl(int tokens, int in_features, int out_features, const void* input
   p.n = tokens;
   p.tmem_cols = tmem_cols_for(tokens);
   p.status = status_word();
+#ifdef IEX_TC_PROFILE
+  p.prof = g_tc_prof_buffer;
+#endif
   st = bind_workspace(p, 1, parts, workspace, bytes);
   if (st) return st;
   const int stages = dense_stages(tokens, kMaxStages);
