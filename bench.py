@@ -432,18 +432,23 @@ def run_ours(args) -> None:
                 out.record_stream(out_stream)
         cur.wait_stream(out_stream)
 
-    for _ in range(min(args.warmup, 3)):
+    for _ in range(max(args.warmup, 10)):  # the pinned staging path takes several passes to settle
         e2e_step()
     barrier()
-    e_start = torch.cuda.Event(enable_timing=True)
-    e_stop = torch.cuda.Event(enable_timing=True)
+    # The host side of this region (pinned-memory copies over PCIe) shares the machine with
+    # other jobs, so it is timed three times and the median repetition is reported; all three
+    # times are in the line.
     e2e_steps = max(1, min(args.steps, 10))
-    e_start.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e_stop.record()
-    barrier()
-    e2e_ms = e_start.elapsed_time(e_stop)
+    e2e_reps = []
+    for _ in range(3):
+        e_start = torch.cuda.Event(enable_timing=True)
+        e_stop = torch.cuda.Event(enable_timing=True)
+        e_start.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e_stop.record()
+        barrier()
+        e2e_reps.append(e_start.elapsed_time(e_stop))
     clocks = sampler.stop() if rank == 0 else None
     # the end-to-end path ran the same kernels on the same inputs as the device-resident one
     # (bit for bit when both ran the same SDDMM kernel, else within the fp32 bar)
@@ -454,9 +459,9 @@ def run_ours(args) -> None:
     assert e2e_same, "end-to-end results differ from the device-resident results"
 
     if dist is not None:
-        tt = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
+        tt = torch.tensor([elapsed_ms, *e2e_reps], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = float(tt[0]), float(tt[1])
+        elapsed_ms, e2e_reps = float(tt[0]), [float(v) for v in tt[1:]]
         fl = torch.tensor([float(total_flops)], device=dev, dtype=torch.float64)
         dist.all_reduce(fl, op=dist.ReduceOp.SUM)
         job_flops = float(fl[0])
@@ -479,6 +484,7 @@ def run_ours(args) -> None:
         return
 
     value = job_flops * args.steps / (elapsed_ms * 1e-3) / 1e9
+    e2e_ms = statistics.median(e2e_reps)
     e2e_value = job_flops * e2e_steps / (e2e_ms * 1e-3) / 1e9
     peak, peak_kind = measured_peak_gbs()
     sddmm_bytes = syn.sddmm_bytes(M, N_COLS, K_DIM, mean_nnz)
@@ -526,7 +532,7 @@ def run_ours(args) -> None:
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": config_dict(world), "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps},
+                "steps": e2e_steps, "ms_of_3_repetitions": e2e_reps},
         "gpu_launches": args.steps * INSTANCES * 2, "clocks": clocks, "kernels": kernels,
         "other_configs": other, "row_split": row_split, "fused_layer": fused_layer, "ffn_stack": ffn,
     }
