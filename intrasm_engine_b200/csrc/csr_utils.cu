@@ -114,26 +114,45 @@ row_fill_kernel(int m, int k, const T* __restrict__ dense, int relu, const int* 
   }
 }
 
-// One CTA per row: clear the dense row with 128-bit stores, then scatter the row's nonzeros.
+// CTA (x, y) owns the columns [y * slice, (y + 1) * slice) of rows x, x + gridDim.x, ...: it
+// clears its piece of the dense row with 128-bit stores and then writes the row's nonzeros
+// that fall into it.  A few CTAs per row instead of one keep each CTA's work down to one or
+// two instructions per thread, so the kernel is as long as its chain of three dependent memory
+// round trips (row offsets, indices and values, stores) and no longer; the row's offsets and
+// its first indices and values are requested before the clearing stores, not after.
 template <typename IT>
 __global__ void __launch_bounds__(256)
-csr_to_dense_f16_kernel(int m, int k, const int* __restrict__ row_offsets, const IT* __restrict__ cols,
+csr_to_dense_f16_kernel(int m, int k, int slice, const int* __restrict__ row_offsets, const IT* __restrict__ cols,
                         const __half* __restrict__ values, __half* __restrict__ out) {
   grid_dependency_wait();  // `out` may still be read by the kernel before this one
   grid_launch_dependents();
+  const int c0 = blockIdx.y * slice;
+  const int c1 = c0 + slice < k ? c0 + slice : k;
+  const bool vec = (k & 7) == 0 && (slice & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
   for (int r = blockIdx.x; r < m; r += gridDim.x) {
     __half* row = out + static_cast<size_t>(r) * k;
-    if ((k & 7) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0) {
+    const int beg = __ldg(row_offsets + r), end = __ldg(row_offsets + r + 1);
+    int p = beg + threadIdx.x;
+    int c = -1;
+    __half v = __float2half(0.f);
+    if (p < end) {
+      c = to_index(__ldg(cols + p));
+      v = __ldg(values + p);
+    }
+    if (vec) {
       uint4* row4 = reinterpret_cast<uint4*>(row);
-      for (int i = threadIdx.x; i < (k >> 3); i += blockDim.x) row4[i] = make_uint4(0u, 0u, 0u, 0u);
+      for (int i = (c0 >> 3) + threadIdx.x; i < (c1 >> 3); i += blockDim.x) row4[i] = make_uint4(0u, 0u, 0u, 0u);
     } else {
-      for (int i = threadIdx.x; i < k; i += blockDim.x) row[i] = __float2half(0.f);
+      for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) row[i] = __float2half(0.f);
     }
     __syncthreads();
-    const int beg = __ldg(row_offsets + r), end = __ldg(row_offsets + r + 1);
-    for (int p = beg + threadIdx.x; p < end; p += blockDim.x) {
-      const int c = to_index(__ldg(cols + p));
-      if (c < k) row[c] = __ldg(values + p);
+    while (p < end) {
+      if (c >= c0 && c < c1) row[c] = v;
+      p += blockDim.x;
+      if (p < end) {
+        c = to_index(__ldg(cols + p));
+        v = __ldg(values + p);
+      }
     }
     __syncthreads();
   }
@@ -211,12 +230,20 @@ extern "C" int iex_csr_to_dense_f16(int m, int k, const int32_t* row_offsets, co
   if (m == 0 || k == 0) return IEX_OK;
   if (!row_offsets || !out) return IEX_ERR_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = m < 4 * kNumSMs ? m : 4 * kNumSMs;
+  // about eight CTAs of 256 threads per SM in all: rows first, then up to eight column slices
+  // (multiples of 8 columns) per row
+  const int gx = m < 8 * kNumSMs ? m : 8 * kNumSMs;
+  int slices = (8 * kNumSMs) / gx;
+  slices = slices < 1 ? 1 : (slices > 8 ? 8 : slices);
+  int slice = ((k + slices - 1) / slices + 7) & ~7;
+  if (slice < 256) slice = 256 < k ? 256 : ((k + 7) & ~7);
+  const int gy = (k + slice - 1) / slice;
+  const dim3 grid(gx, gy);
   if (index_bits == 16)
-    return launch_overlapped(csr_to_dense_f16_kernel<uint16_t>, dim3(grid), dim3(256), 0, s, m, k, row_offsets,
+    return launch_overlapped(csr_to_dense_f16_kernel<uint16_t>, grid, dim3(256), 0, s, m, k, slice, row_offsets,
                              static_cast<const uint16_t*>(column_indices), static_cast<const __half*>(values),
                              static_cast<__half*>(out));
-  return launch_overlapped(csr_to_dense_f16_kernel<int>, dim3(grid), dim3(256), 0, s, m, k, row_offsets,
+  return launch_overlapped(csr_to_dense_f16_kernel<int>, grid, dim3(256), 0, s, m, k, slice, row_offsets,
                            static_cast<const int*>(column_indices), static_cast<const __half*>(values),
                            static_cast<__half*>(out));
 }
