@@ -1054,6 +1054,20 @@ def profile_kernel(which: str) -> None:
         ws = [up(np.ascontiguousarray(w.T)) for _ in range(2)]
         for i in range(4):
             layer(va, ro, ci, ws[i % 2])
+    elif which == "spmm_f32_tc":
+        # the fp32 tensor-core SpMM on the config-2 mask with stand-in values (12 instances > L2)
+        runs = []
+        for i in range(12):
+            mask, q, k, v = syn.sddmm_chain_case(i, M, N_COLS, K_DIM, DENSITY)
+            ro, ci = up(mask.row_offsets), up(mask.column_indices)
+            plan = torch.ops.iex_ops.spmm_plan(ro, ci, M, N_COLS)
+            need = _lib.lib.iex_spmm_f32_tc_workspace_bytes(M, N_COLS, K_DIM)
+            runs.append((mask.nnz, plan, torch.randn(mask.nnz, device=dev), up(v),
+                         torch.empty((M, K_DIM), device=dev), torch.empty(max(int(need), 16), dtype=torch.uint8, device=dev)))
+        for _ in range(2):
+            for nnz, plan, vals, v, o, ws in runs:
+                _lib.call("iex_spmm_f32_tc", M, N_COLS, K_DIM, nnz, plan.data_ptr(), vals.data_ptr(), v.data_ptr(),
+                          o.data_ptr(), ws.data_ptr(), ws.numel(), st)
     elif which in ("sddmm", "spmm", "sddmm_tc"):
         runs = []
         for i in range(12):  # 12 x 11 MB > L2
@@ -1103,7 +1117,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-kernel", default=None,
-                    choices=["sddmm", "sddmm_tc", "spmm", "linear", "spmm_tc", "fused", "ffn"],
+                    choices=["sddmm", "sddmm_tc", "spmm", "spmm_f32_tc", "linear", "spmm_tc", "fused", "ffn"],
                     help="run a few launches of one kernel on its benchmark workload and exit")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the sections beside the primary workload (used for profiler captures)")
