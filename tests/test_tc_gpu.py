@@ -418,10 +418,18 @@ def test_spmm_tc_and_fused_splitk(oracle, parts):
     _status_clean()
 
 
-@pytest.mark.parametrize("m,k,idx", [(256, 11008, np.int32), (33, 100, np.int16), (5, 7, np.int32)])
+@pytest.mark.parametrize("m,k,idx", [(256, 11008, np.int32), (33, 100, np.int16), (5, 7, np.int32),
+                                     (2000, 520, np.int16), (64, 4096, np.int16), (1, 8, np.int32),
+                                     (300, 2056, np.int32)])
 def test_csr_to_dense(m, k, idx):
+    """Shapes on both sides of every split the kernel makes: more rows than resident CTAs, one
+    to eight column slices per row, k with and without the 8-column alignment of the vector
+    stores, rows that are empty, full and longer than a block's first pass."""
     rng = np.random.default_rng(m + k)
-    a = syn.csr_from_mask(rng.random((m, k)) < 0.1, rng=rng, std=1.0, dtype=np.float16, index_dtype=idx)
+    mask = rng.random((m, k)) < 0.1
+    mask[0] = True
+    mask[m // 2] = False
+    a = syn.csr_from_mask(mask, rng=rng, std=1.0, dtype=np.float16, index_dtype=idx)
     da = G.DevCSR(a)
     out = torch.full((m, k), 7.0, dtype=torch.float16, device=G.DEV)
     _lib.call("iex_csr_to_dense_f16", m, k, da.row_offsets.data_ptr(), G.ptr(da.column_indices),
