@@ -63,8 +63,8 @@ def test_linear_golden(oracle, golden_dir):
 @pytest.mark.parametrize("tokens,cin,cout", [(16, 8, 8), (16, 64, 128), (64, 128, 128), (64, 256, 384),
                                              (32, 520, 200), (128, 1024, 1000), (256, 328, 640),
                                              (48, 4096, 256), (64, 4096, 12288),
-                                             # from 128 tokens on a unit holds two 128-row tiles that
-                                             # share the X stage (even, odd and single tile counts)
+                                             # 128 tokens and more: 64- and 96-KB stages, two-deep ring
+                                             # (even, odd and single tile counts)
                                              (128, 512, 512), (192, 776, 384), (256, 2048, 1000),
                                              (256, 11008, 640), (256, 64, 128), (144, 1024, 300)])
 def test_linear_shapes(tokens, cin, cout):
