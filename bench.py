@@ -766,6 +766,19 @@ def other_configs_section(dev):
                 if (rows, cols, sparsity, n) in ((512, 512, 0.9, 256), (2048, 512, 0.7, 128), (512, 2048, 0.95, 128)):
                     cold = {"cuda_core_us_cold_single_launch": round(_cold_launch_us(simt, 5), 2),
                             "tensor_core_us_cold_single_launch": round(_cold_launch_us(tc, 5), 2)}
+                    # the op's batch dimension (reuse_weight: one A, eight dense operands, one launch)
+                    nb3 = 8
+                    b8 = [(torch.randn((nb3, cols, n), device=dev).half(),
+                           torch.empty((nb3, rows, n), dtype=torch.float16, device=dev)) for _ in range(6)]
+
+                    def simt_b(i):
+                        ri, va, ro, ci, _bb, _o = c3s[i % copies3]
+                        bb, o = b8[i % 6]
+                        _lib.call("iex_spmm_f16_i16", rows, cols, n, a3.nnz, ri.data_ptr(), va.data_ptr(),
+                                  ro.data_ptr(), ci.data_ptr(), bb.data_ptr(), None, o.data_ptr(), nb3, st)
+
+                    cold["cuda_core_batch8_us_per_instance"] = round(_time_us(simt_b, iters=48, warmup=12) / nb3, 2)
+                    del b8
                 pick = tuning.choose_spmm_kernel(rows, cols, n, a3.nnz)
                 t_pick = t_tc if pick == "tensor_core" else t_simt
                 best = min(t_simt, t_tc)
