@@ -129,6 +129,19 @@ IEX_API int iex_sddmm_plan_build(int m, int n, int nnz, const int32_t* row_offse
                                  void* stream);
 IEX_API int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, const float* lhs,
                              const float* rhs, float* out, int accumulate, void* stream);
+
+/* Several products of one shape (m, k, n) in ONE launch: problem i has its own lhs[i], rhs[i],
+ * outs[i], nnz[i] and plans[i] (host arrays of `count` entries, count <= iex_sddmm_f32_tc_max_batch()).
+ * The kernel's fixed costs (launch, the first lhs band, the last tile's read-out) are paid once
+ * and a CTA loads its next unit's lhs band while the tensor core works on the current one:
+ * the heads of a sparse attention layer, or the independent instances of a throughput job.
+ * Results equal `count` calls of iex_sddmm_f32_tc bit for bit.  No counterpart in the
+ * reference, whose batch dimension sums the products into one vector (sputnik_sddmm.cu.inc:177-178). */
+IEX_API int iex_sddmm_f32_tc_batched(int count, int m, int k, int n, const int* nnz,
+                                     const void* const* plans, const float* const* lhs,
+                                     const float* const* rhs, float* const* outs, int accumulate,
+                                     void* stream);
+IEX_API int iex_sddmm_f32_tc_max_batch(void);
 IEX_API int iex_sddmm_f32_tc_supported(int m, int k, int n, int batch);
 IEX_API int iex_sddmm_f32_prefers_tc(int m, int k, int n, int nnz, int batch);
 

@@ -35,6 +35,11 @@ SIGNATURES = {
     # m k n nnz row_indices row_offsets cols index_bits lhs rhs out batch stream
     "iex_sddmm_f16": (c_int, [c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr,
                               c_ptr, c_int, c_ptr]),
+    # count m k n nnz[] plans[] lhs[] rhs[] outs[] accumulate stream
+    "iex_sddmm_f32_tc_batched": (c_int, [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_ptr),
+                                         ctypes.POINTER(c_ptr), ctypes.POINTER(c_ptr), ctypes.POINTER(c_ptr),
+                                         c_int, c_ptr]),
+    "iex_sddmm_f32_tc_max_batch": (c_int, []),
     # m n nnz
     "iex_sddmm_plan_bytes": (c_size, [c_int, c_int, c_int]),
     # m n nnz row_offsets cols plan plan_bytes stream

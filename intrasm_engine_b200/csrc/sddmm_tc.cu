@@ -69,24 +69,35 @@ constexpr int kBarBytes = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemAHi = 384, kTmemALo = 448;
 
-struct Params {
-  int m, n, k, nnz;
+constexpr int kMaxProblems = 32;  // products of one launch (same shape, own operands and plan)
+
+struct Problem {
   const int* tile_ptr;         // [bands * tiles_per_band + 1]
   const uint16_t* entry;       // [nnz] (row in tile << 7) | column in tile
   const int* dest;             // [nnz] position in storage order
   const float* lhs;
   const float* rhs;
   float* out;
+};
+
+struct Params {
+  int m, n, k;
+  int count;                   // problems in this launch
+  Problem prob[kMaxProblems];
   int accumulate;
   int tiles_per_band;
-  // units: bands [0, bands_hi) are cut into base_splits + 1 runs of tiles, the others into
-  // base_splits runs; CTA c takes units c, c + grid, ...
+  // units of ONE problem: bands [0, bands_hi) are cut into base_splits + 1 runs of tiles, the
+  // others into base_splits runs; the launch's units are those of problem 0, then problem 1, ...
+  // and CTA c takes units c, c + grid, ...  A CTA that takes several units loads the next
+  // unit's lhs band while the tensor core works on the current one.
   int units, base_splits, bands_hi;
   int* status;
   IEX_PROF_FIELD
 };
 
-__device__ __forceinline__ void unit_of(int u, const Params& p, int& band, int& t0, int& t1) {
+__device__ __forceinline__ void unit_of(int u_all, const Params& p, int& pi, int& band, int& t0, int& t1) {
+  pi = u_all / p.units;
+  const int u = u_all - pi * p.units;
   const int hi_units = p.bands_hi * (p.base_splits + 1);
   int s, S;
   if (u < hi_units) {
@@ -263,11 +274,13 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
     uint32_t off[NVB];
     plane_offsets<NVB, kAtomBytesB>(off, kv_shift, ct);
     IEX_PROF_BEGIN
-    for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x, ++ui) {
-      int band, t0, t1;
-      unit_of(u, prm, band, t0, t1);
+    const int total_units = prm.units * prm.count;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+      int pi, band, t0, t1;
+      unit_of(u, prm, pi, band, t0, t1);
+      const float* __restrict__ rhs = prm.prob[pi].rhs;
       float4 v[NVB];
-      load_rows<NVB>(v, prm.rhs, t0 * TN, prm.n, k, kv_shift, ct);  // first tile: in flight meanwhile
+      load_rows<NVB>(v, rhs, t0 * TN, prm.n, k, kv_shift, ct);  // first tile: in flight meanwhile
       IEX_LAP(0)  // unit start: first rhs loads issued
       for (int t = t0; t < t1; ++t, ++it) {
         const int s = it % kBStages;
@@ -278,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(b_full(s));
-        if (t + 1 < t1) load_rows<NVB>(v, prm.rhs, (t + 1) * TN, prm.n, k, kv_shift, ct);
+        if (t + 1 < t1) load_rows<NVB>(v, rhs, (t + 1) * TN, prm.n, k, kv_shift, ct);
         IEX_LAP(3)  // fence, arrive, next loads issued
       }
     }
@@ -292,9 +305,10 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
       uint32_t it = 0, ui = 0;
       bool ok = true;
       IEX_PROF_BEGIN
-      for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x, ++ui) {
-        int band, t0, t1;
-        unit_of(u, prm, band, t0, t1);
+      const int total_units = prm.units * prm.count;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+        int pi, band, t0, t1;
+        unit_of(u, prm, pi, band, t0, t1);
         if (!mbar_wait(a_full, ui & 1u, abort_flag, prm.status, 32)) { ok = false; break; }
         IEX_LAP(0)  // waiting for the lhs band
         for (int t = t0; t < t1; ++t, ++it) {
@@ -334,11 +348,8 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
     const int q = warp & 3;                       // TMEM lane quarter
     const int half = ew >> 2;                     // which 64 columns of the tile this warp copies
     const uint32_t park_row = park_base + static_cast<uint32_t>(q * 32 + lane) * kParkStride + half * 256;
-    const int* __restrict__ tile_ptr = prm.tile_ptr;
-    const uint16_t* __restrict__ entry = prm.entry;
-    const int* __restrict__ dest = prm.dest;
-    float* __restrict__ out = prm.out;
     const int T = prm.tiles_per_band;
+    const int total_units = prm.units * prm.count;
     uint32_t it = 0, sync_it = 0;
     bool ok = true;
     IEX_PROF_BEGIN
@@ -352,9 +363,13 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
       return done;
     };
     uint32_t ui = 0;
-    for (int u = blockIdx.x; u < prm.units && ok; u += gridDim.x, ++ui) {
-      int band, t0, t1;
-      unit_of(u, prm, band, t0, t1);
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++ui) {
+      int pi, band, t0, t1;
+      unit_of(u, prm, pi, band, t0, t1);
+      const int* __restrict__ tile_ptr = prm.prob[pi].tile_ptr;
+      const uint16_t* __restrict__ entry = prm.prob[pi].entry;
+      const int* __restrict__ dest = prm.prob[pi].dest;
+      float* __restrict__ out = prm.prob[pi].out;
       int e_beg = __ldg(tile_ptr + band * T + t0), e_end = __ldg(tile_ptr + band * T + t0 + 1);
       // The unit's lhs band into tensor memory: thread = row (TMEM lane), this warp's half of
       // k, all loads of the row in flight together.  The epilogue warps do it because they sit
@@ -362,7 +377,8 @@ __global__ void __launch_bounds__(kThreads, 1) sddmm_tc_kernel(const Params prm)
       {
         const int row = band * TM + q * 32 + lane;
         constexpr int kHalf = KA * 16;  // k-values per warp: 32 for k = 64, 16 for k = 32
-        const float4* src = reinterpret_cast<const float4*>(prm.lhs + static_cast<size_t>(row) * k + half * kHalf);
+        const float4* src =
+            reinterpret_cast<const float4*>(prm.prob[pi].lhs + static_cast<size_t>(row) * k + half * kHalf);
         float4 x[kHalf / 4];
 #pragma unroll
         for (int j = 0; j < kHalf / 4; ++j) {
@@ -510,7 +526,8 @@ int launch(Params prm, cudaStream_t stream) {
     }
   }
   const int sms = sm_count();
-  const int grid = prm.units < sms ? prm.units : sms;
+  const int total = prm.units * prm.count;
+  const int grid = total < sms ? total : sms;
   return launch_overlapped(kern, dim3(grid), dim3(kThreads), smem, stream, prm);
 }
 
@@ -535,27 +552,42 @@ static long long* g_prof_buffer = nullptr;
 extern "C" void iex_sddmm_f32_tc_set_profile_buffer(long long* device_buffer) { g_prof_buffer = device_buffer; }
 #endif
 
-extern "C" int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, const float* lhs,
-                                const float* rhs, float* out, int accumulate, void* stream) {
+namespace {
+
+// One launch over `count` products of the same shape (m, k, n), each with its own operands,
+// result, number of stored positions and plan.
+int sddmm_tc_launch(int m, int k, int n, int count, const int* nnz, const void* const* plans,
+                    const float* const* lhs, const float* const* rhs, float* const* outs, int accumulate,
+                    void* stream) {
   using namespace iex;
   using namespace iex::sddmm_tc;
-  if (m < 0 || k < 0 || n < 0 || nnz < 0) return IEX_ERR_BAD_ARG;
-  if (m == 0 || nnz == 0) return IEX_OK;
-  if (!plan || !lhs || !rhs || !out || !aligned16(plan)) return IEX_ERR_BAD_ARG;
-  if (!iex_sddmm_f32_tc_supported(m, k, n, 1) || !aligned16(lhs) || !aligned16(rhs)) return IEX_ERR_UNSUPPORTED;
-  const tile_plan::Layout L = tile_plan::layout(m, n, nnz, TN);
-  const uint8_t* base = static_cast<const uint8_t*>(plan);
+  if (m < 0 || k < 0 || n < 0 || count < 0 || count > kMaxProblems) return IEX_ERR_BAD_ARG;
+  if (m == 0 || count == 0) return IEX_OK;
+  if (!nnz || !plans || !lhs || !rhs || !outs) return IEX_ERR_BAD_ARG;
+  if (!iex_sddmm_f32_tc_supported(m, k, n, 1)) return IEX_ERR_UNSUPPORTED;
   Params p{};
   p.m = m;
   p.n = n;
   p.k = k;
-  p.nnz = nnz;
-  p.tile_ptr = reinterpret_cast<const int*>(base + L.tile_ptr);
-  p.entry = reinterpret_cast<const uint16_t*>(base + L.entry);
-  p.dest = reinterpret_cast<const int*>(base + L.dest);
-  p.lhs = lhs;
-  p.rhs = rhs;
-  p.out = out;
+  int used = 0;
+  tile_plan::Layout L{};
+  for (int i = 0; i < count; ++i) {
+    if (nnz[i] < 0) return IEX_ERR_BAD_ARG;
+    if (nnz[i] == 0) continue;  // nothing stored: nothing to write
+    if (!plans[i] || !lhs[i] || !rhs[i] || !outs[i] || !aligned16(plans[i])) return IEX_ERR_BAD_ARG;
+    if (!aligned16(lhs[i]) || !aligned16(rhs[i])) return IEX_ERR_UNSUPPORTED;
+    L = tile_plan::layout(m, n, nnz[i], TN);
+    const uint8_t* base = static_cast<const uint8_t*>(plans[i]);
+    Problem& q = p.prob[used++];
+    q.tile_ptr = reinterpret_cast<const int*>(base + L.tile_ptr);
+    q.entry = reinterpret_cast<const uint16_t*>(base + L.entry);
+    q.dest = reinterpret_cast<const int*>(base + L.dest);
+    q.lhs = lhs[i];
+    q.rhs = rhs[i];
+    q.out = outs[i];
+  }
+  if (used == 0) return IEX_OK;
+  p.count = used;
   p.accumulate = accumulate;
   p.status = tc::status_word();
 #ifdef IEX_TC_PROFILE
@@ -575,3 +607,21 @@ extern "C" int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return k == 32 ? launch<1>(p, s) : launch<2>(p, s);
 }
+
+}  // namespace
+
+extern "C" int iex_sddmm_f32_tc(int m, int k, int n, int nnz, const void* plan, const float* lhs,
+                                const float* rhs, float* out, int accumulate, void* stream) {
+  if (nnz < 0) return IEX_ERR_BAD_ARG;
+  if (m == 0 || nnz == 0) return IEX_OK;
+  if (!plan || !lhs || !rhs || !out) return IEX_ERR_BAD_ARG;
+  return sddmm_tc_launch(m, k, n, 1, &nnz, &plan, &lhs, &rhs, &out, accumulate, stream);
+}
+
+extern "C" int iex_sddmm_f32_tc_batched(int count, int m, int k, int n, const int* nnz, const void* const* plans,
+                                        const float* const* lhs, const float* const* rhs, float* const* outs,
+                                        int accumulate, void* stream) {
+  return sddmm_tc_launch(m, k, n, count, nnz, plans, lhs, rhs, outs, accumulate, stream);
+}
+
+extern "C" int iex_sddmm_f32_tc_max_batch(void) { return iex::sddmm_tc::kMaxProblems; }

@@ -84,7 +84,13 @@ class MyAutogradFunc(torch.autograd.Function):
 
     @classmethod
     def run(cls, *args, **fwd_kwargs):
-        """``apply`` with keyword dictionaries (``fwd_kwargs_1=...``; defaults when omitted)."""
+        """``apply`` with keyword dictionaries (``fwd_kwargs_1=...``; defaults when omitted).
+        A class that has not been through ``make_single_kernel_autograd_function`` yet (the
+        factory of horizontal_rewriter that builds ``forward`` / ``backward`` from ``_forward`` /
+        ``_backward``) is put through it here, so that ``run`` works whatever was imported first."""
+        if "forward" not in cls.__dict__:
+            from ....pytorch.horizontal_rewriter import make_single_kernel_autograd_function
+            make_single_kernel_autograd_function(cls)
         if not fwd_kwargs:
             fwd_kwargs = {"fwd_kwargs_1": default_fwd_kwargs()}
         return cls.apply(fwd_kwargs, *args)

@@ -331,3 +331,45 @@ def test_sddmm_half_torch_op_and_fp16_backward(oracle):
     direct = torch.ops.iex_ops.sddmm_sputnik_half(grad[None], b.detach()[None], da.row_indices, da.row_offsets,
                                                   da.column_indices)
     assert torch.equal(direct, values.grad)
+
+
+def test_sddmm_tc_batched_equals_single_launches(oracle):
+    """Several products of one shape in one launch (own operands, masks and plans; one of them
+    with an empty mask): every result equals its single launch bit for bit, CTAs that take more
+    than one unit included (6 problems x 32 units on 148 SMs)."""
+    import ctypes
+    from intrasm_engine_b200 import _lib
+    m, n, k, count = 1024, 2048, 64, 6
+    rng = np.random.default_rng(21)
+    probs = []
+    for i in range(count):
+        dens = 0.0 if i == 2 else 0.03 + 0.02 * i
+        mask = syn.csr_from_mask(rng.random((m, n)) < dens, rng=rng)
+        dm = G.DevCSR(mask)
+        lhs = G.dev(rng.standard_normal((m, k)).astype(np.float32))
+        rhs = G.dev(rng.standard_normal((n, k)).astype(np.float32))
+        plan = G.sddmm_plan(dm, n)
+        single = G.sddmm_f32_tc(dm, lhs, rhs, plan=plan) if mask.nnz else torch.empty(0, device=G.DEV)
+        probs.append((mask, dm, lhs, rhs, plan, single, torch.full((max(mask.nnz, 1),), 7.0, device=G.DEV)))
+    P = ctypes.c_void_p * count
+    nnz = (ctypes.c_int * count)(*[p[0].nnz for p in probs])
+    _lib.call("iex_sddmm_f32_tc_batched", count, m, k, n, nnz, P(*[p[4].data_ptr() for p in probs]),
+              P(*[p[2].data_ptr() for p in probs]), P(*[p[3].data_ptr() for p in probs]),
+              P(*[p[6].data_ptr() for p in probs]), 0, G.stream_ptr())
+    torch.cuda.synchronize()
+    assert _lib.lib.iex_last_device_status(1) == 0
+    for mask, dm, lhs, rhs, plan, single, out in probs:
+        if mask.nnz == 0:
+            assert float(out[0]) == 7.0  # untouched
+            continue
+        assert torch.equal(out, single)
+        exact = oracle.sddmm(lhs.cpu().numpy()[None], rhs.cpu().numpy()[None], mask.row_indices, mask.row_offsets,
+                             mask.column_indices, f64=True)
+        sabs = oracle.sddmm(np.abs(lhs.cpu().numpy())[None], np.abs(rhs.cpu().numpy())[None], mask.row_indices,
+                            mask.row_offsets, mask.column_indices, f64=True)
+        assert G.sddmm_close(out.cpu().numpy(), exact, sabs)
+    too_many = _lib.lib.iex_sddmm_f32_tc_max_batch() + 1
+    big = (ctypes.c_void_p * too_many)()
+    st = _lib.lib.iex_sddmm_f32_tc_batched(too_many, m, k, n, (ctypes.c_int * too_many)(), big, big, big, big, 0,
+                                           G.stream_ptr())
+    assert st == -1  # IEX_ERR_BAD_ARG
