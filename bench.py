@@ -62,7 +62,7 @@ def config_dict(n_gpus: int) -> dict:
         "instances_per_gpu": INSTANCES,
         "l2_policy": "inputs > L2: a step streams %d instances (~270 MB)" % INSTANCES,
         "index_dtype": "int32",
-        "sddmm": "value: tensor cores with the mask's plan (pattern-only, prebuilt like row_indices); e2e: reference op, CUDA cores, no plan",
+        "sddmm": "value: tensor cores + prebuilt pattern plan; e2e: reference op, no plan",
         "parallelism": "instances per GPU, no collective" if n_gpus > 1 else "single GPU",
     }
 
@@ -586,7 +586,7 @@ def run_ours(args) -> None:
         "gpu_launches": args.steps * INSTANCES * 2, "clocks": clocks, "kernels": kernels,
         "two_streams": {"value": job_flops * args.steps / (overlapped_ms * 1e-3) / 1e9, "unit": UNIT,
                         "ms_per_step": overlapped_ms / args.steps,
-                        "note": "same step, instances alternating over 2 streams (SDDMM of one overlaps SpMM of another)"},
+                        "note": "same step, instances alternate over 2 streams"},
         "other_configs": other, "row_split": row_split, "fused_layer": fused_layer, "ffn_stack": ffn,
     }
     emit(line, details)
